@@ -1,0 +1,215 @@
+"""The one step function.
+
+A step is a batch of sequences that either all start (their prompts, of unequal lengths, packed
+back to back) or all go on by one token.  It runs only the tokens it is given, as one batch, from
+the cache that earlier steps left, and returns 32-bit logits at the wanted places.  Sequence ``b``
+appends ``q_len[b]`` tokens at positions ``len .. len + q_len - 1`` of its slot, and the token at
+position ``p`` sees keys ``0..p`` — the reference's chain semantics
+(``engine/dryft_qwen3/model.py:307-318``; ``kernels/attn_decode.py:46-63``), which make prefill, chunked
+prefill and decode the same operation.  The reference has two entry points instead (equal-length
+``prefill`` groups and ``decode_step``, ``model.py:123,191``) and runs ragged batches as several
+prefills (``engine/engine.py:172-186``).
+
+Padding: a decode batch may be padded to a captured size with sequences whose slot is -1; every
+kernel skips them, so padding changes no result.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+from ..cache.store import SequenceCache
+from ..ops import kernels as K
+from ..parts.attention import PREFILL_TILE
+from ..parts.base import Runtime, StepContext
+from .model import DecoderModel
+
+
+class Stepper:
+    def __init__(self, model: DecoderModel, cache: SequenceCache, rt: Runtime, cuda_graphs: bool = True):
+        self.model = model
+        self.cache = cache
+        self.rt = rt
+        self.cuda_graphs = cuda_graphs
+        self._graphs: Dict[int, "_DecodeGraph"] = {}
+        self._pinned: Optional[torch.Tensor] = None
+        self._upload_event: Optional[torch.cuda.Event] = None
+
+    # ------------------------------------------------------------------ host -> device metadata
+    def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], want: Sequence[Sequence[int]]) -> Optional[torch.Tensor]:
+        """``slots[b]`` appends ``tokens[b]``; logits are returned for ``want[b]`` (indices into
+        ``tokens[b]``), in the order of the sequences and of ``want``: ``[n_wanted, vocab]`` float32
+        on the device, or None when nothing is wanted."""
+        B = len(slots)
+        if B == 0:
+            return None
+        if len(tokens) != B or len(want) != B:
+            raise ValueError("step: slots, tokens and want must have one entry per sequence")
+        vocab = self.model.vocab_size
+        q_lens = [len(t) for t in tokens]
+        if any(q == 0 for q in q_lens):
+            raise ValueError("step: every sequence of a step brings at least one token")
+        if len(set(slots)) != B:
+            raise ValueError("step: a slot occurs twice in one step")
+        cu = [0]
+        flat: List[int] = []
+        for t in tokens:
+            for v in t:
+                if not 0 <= int(v) < vocab:
+                    raise ValueError(f"step: token id {v} is outside the vocabulary [0, {vocab})")
+            flat.extend(int(v) for v in t)
+            cu.append(len(flat))
+        rows: List[int] = []
+        for b, w in enumerate(want):
+            for i in w:
+                if not 0 <= int(i) < q_lens[b]:
+                    raise ValueError(f"step: wanted place {i} is outside the {q_lens[b]} tokens of sequence {b}")
+                rows.append(cu[b] + int(i))
+        decode = all(q == 1 for q in q_lens)
+        starts = [self.cache.len_host[s] for s in slots]
+
+        for s, q in zip(slots, q_lens):
+            self.cache.reserve(s, q)
+        self.cache.flush()
+
+        N = len(flat)
+        tiles0: List[int] = []
+        tilesn: List[int] = []
+        if not decode:
+            order = []
+            for b, q in enumerate(q_lens):
+                for q0 in range(0, q, PREFILL_TILE):
+                    order.append((starts[b] + q0, cu[b] + q0, min(PREFILL_TILE, q - q0)))
+            order.sort(key=lambda t: -t[0])  # tiles with the most keys first
+            tiles0 = [t[1] for t in order]
+            tilesn = [t[2] for t in order]
+        T = len(tiles0)
+        W = len(rows)
+        packed = flat + cu + list(slots) + rows + tiles0 + tilesn
+        dev = self._upload(packed)
+        o = 0
+        d_tokens = dev[o:o + N]; o += N
+        d_cu = dev[o:o + B + 1]; o += B + 1
+        d_slot = dev[o:o + B]; o += B
+        d_rows = dev[o:o + W]; o += W
+        d_t0 = dev[o:o + T]; o += T
+        d_tn = dev[o:o + T]; o += T
+        meta = torch.empty(2 * N, dtype=torch.int32, device=self.rt.device)
+        tok_slot, tok_pos = meta[:N], meta[N:]
+        K.step_meta(d_cu, d_slot, self.cache.seq_len, tok_slot, tok_pos, N, B)
+        ctx = StepContext(n_tokens=N, n_seqs=B, tokens=d_tokens, cu_q=d_cu, seq_slot=d_slot, tok_slot=tok_slot,
+                          tok_pos=tok_pos, decode=decode, tile_tok0=d_t0 if T else None, tile_rows=d_tn if T else None,
+                          n_tiles=T, tile_size=PREFILL_TILE)
+        logits = self.model.forward(ctx, self.cache, d_rows if W else None, W)
+        K.step_advance(d_cu, d_slot, self.cache.seq_len, B)
+        for s, q in zip(slots, q_lens):
+            self.cache.advanced(s, q)
+        return logits
+
+    def _upload(self, ints: List[int]) -> torch.Tensor:
+        """One host->device copy of the step's integers through pinned memory."""
+        n = len(ints)
+        if self._pinned is None or self._pinned.numel() < n:
+            self._pinned = torch.empty(max(n, 4096), dtype=torch.int32, pin_memory=True)
+        # the previous step's copy out of this buffer must have finished before it is rewritten
+        if self._upload_event is not None:
+            self._upload_event.synchronize()
+        buf = self._pinned[:n]
+        buf.copy_(torch.tensor(ints, dtype=torch.int32))
+        dev = torch.empty(n, dtype=torch.int32, device=self.rt.device)
+        dev.copy_(buf, non_blocking=True)
+        self._upload_event = torch.cuda.Event()
+        self._upload_event.record()
+        return dev
+
+    # ------------------------------------------------------------------ decode from the device state
+    def decode_from_state(self, slots: Sequence[int]) -> torch.Tensor:
+        """One decode step whose input tokens are the sequences' last chosen tokens, kept on the
+        device (``SequenceCache.last_token``).  Returns logits ``[bucket, vocab]``; rows beyond
+        ``len(slots)`` belong to padding.  Replays a captured CUDA graph of the step when enabled
+        (one graph per batch size serves every position, because lengths are read on the device —
+        ``engine/dryft_qwen3/cache.py:8-10``; ``graphs.py:108-135``)."""
+        B = len(slots)
+        for s in slots:
+            self.cache.reserve(s, 1)
+        self.cache.flush()
+        bucket = _bucket(B)
+        g = self._graphs.get(bucket)
+        if g is None:
+            g = _DecodeGraph(self, bucket)
+            self._graphs[bucket] = g
+        logits = g.run(slots)
+        for s in slots:
+            self.cache.advanced(s, 1)
+        return logits
+
+
+def _bucket(b: int) -> int:
+    """Decode batch sizes are padded to 1, 2, 4, 8, then multiples of 8."""
+    if b <= 8:
+        n = 1
+        while n < b:
+            n *= 2
+        return n
+    return (b + 7) // 8 * 8
+
+
+class _DecodeGraph:
+    """Static buffers and (optionally) a captured graph of one decode step at a fixed batch size."""
+
+    def __init__(self, stepper: Stepper, bucket: int):
+        self.st = stepper
+        self.bucket = bucket
+        dev = stepper.rt.device
+        self.slot_host = torch.full((bucket,), -1, dtype=torch.int32).pin_memory()
+        self.seq_slot = torch.full((bucket,), -1, dtype=torch.int32, device=dev)
+        self.cu_q = torch.arange(bucket + 1, dtype=torch.int32, device=dev)
+        self.tokens = torch.zeros(bucket, dtype=torch.int32, device=dev)
+        self.tok_slot = torch.zeros(bucket, dtype=torch.int32, device=dev)
+        self.tok_pos = torch.zeros(bucket, dtype=torch.int32, device=dev)
+        self.rows = torch.arange(bucket, dtype=torch.int32, device=dev)
+        self.logits: Optional[torch.Tensor] = None
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.h2d_bytes = 4 * bucket
+        self._copied: Optional[torch.cuda.Event] = None
+
+    def _body(self) -> torch.Tensor:
+        st = self.st
+        K.tokens_from_state(self.seq_slot, st.cache.last_token, self.tokens, self.bucket)
+        K.step_meta(self.cu_q, self.seq_slot, st.cache.seq_len, self.tok_slot, self.tok_pos, self.bucket, self.bucket)
+        ctx = StepContext(n_tokens=self.bucket, n_seqs=self.bucket, tokens=self.tokens, cu_q=self.cu_q,
+                          seq_slot=self.seq_slot, tok_slot=self.tok_slot, tok_pos=self.tok_pos, decode=True)
+        logits = st.model.forward(ctx, st.cache, self.rows, self.bucket)
+        K.step_advance(self.cu_q, self.seq_slot, st.cache.seq_len, self.bucket)
+        return logits
+
+    def run(self, slots: Sequence[int]) -> torch.Tensor:
+        n = len(slots)
+        if self._copied is not None:
+            self._copied.synchronize()  # the last copy out of the pinned buffer has finished
+        self.slot_host[:n] = torch.tensor(list(slots), dtype=torch.int32)
+        self.slot_host[n:] = -1
+        self.seq_slot.copy_(self.slot_host, non_blocking=True)
+        self._copied = torch.cuda.Event()
+        self._copied.record()
+        if not self.st.cuda_graphs:
+            return self._body()
+        if self.graph is None:
+            # Capture.  Warm-up runs would advance the sequences, so they run on padding only.
+            torch.cuda.synchronize()
+            self.seq_slot.fill_(-1)
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                for _ in range(2):
+                    self._body()
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            self.graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.graph):
+                self.logits = self._body()
+            self.seq_slot.copy_(self.slot_host, non_blocking=True)
+        self.graph.replay()
+        return self.logits

@@ -1,0 +1,371 @@
+"""Python face of the CUDA kernels: loads the compiled libraries with ``ctypes`` and wraps every
+launcher in a function that checks devices, dtypes, shapes and contiguity before the launch.
+
+There is no CPU path and no PyTorch stand-in behind these functions: if the library cannot be
+built or loaded, or a tensor is not on a CUDA device, they raise.  (The reference degrades to a
+PyTorch path when a Triton kernel fails its self-test, ``engine/dryft_qwen3/model.py:104-119``;
+this library fails loudly instead.)
+
+All launches go to PyTorch's current CUDA stream, so they order with PyTorch work and are
+captured by ``torch.cuda.graph``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import threading
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import build
+
+_i, _f, _p, _ll, _ull = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong, ctypes.c_ulonglong
+
+CORE_SOURCES = ("elementwise.cu", "rope_kv.cu", "gemm_f32.cu", "sample.cu", "gemm_small_m.cu")
+UNSUPPORTED = -2
+
+
+class KernelError(RuntimeError):
+    """A launcher refused its arguments or CUDA reported an error at launch."""
+
+
+_lock = threading.Lock()
+_core: Optional[ctypes.CDLL] = None
+_variants: Dict[Tuple, ctypes.CDLL] = {}
+
+
+def _load(path: str) -> ctypes.CDLL:
+    try:
+        return ctypes.CDLL(path)
+    except OSError as e:  # pragma: no cover - depends on the machine
+        raise KernelError(f"cannot load compiled kernels {path}: {e}") from e
+
+
+def core() -> ctypes.CDLL:
+    """The size-independent kernels (metadata, embedding, norms, SiLU*mul, RoPE + cache write,
+    32-bit matrix product, small-batch bf16 matrix product, token choice)."""
+    global _core
+    with _lock:
+        if _core is None:
+            lib = _load(build.build_library("core", CORE_SOURCES))
+            lib.dryft_step_meta.argtypes = [_p, _p, _p, _i, _i, _p, _p, _p]
+            lib.dryft_step_advance.argtypes = [_p, _p, _p, _i, _p]
+            lib.dryft_tokens_from_state.argtypes = [_p, _p, _p, _i, _p]
+            lib.dryft_embed.argtypes = [_i, _p, _p, _p, _i, _i, _i, _p, _p]
+            lib.dryft_rmsnorm.argtypes = [_i, _p, _p, _p, _p, _p, _p, _i, _i, _f, _p]
+            lib.dryft_residual_add.argtypes = [_i, _p, _p, _ll, _p]
+            lib.dryft_silu_mul.argtypes = [_i, _p, _p, _i, _i, _p]
+            lib.dryft_qk_norm_rope_store.argtypes = [_i, _p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i,
+                                                     _i, _i, _f, _i, _i, _p]
+            lib.dryft_gemm_nt_f32.argtypes = [_p, _i, _p, _p, _i, _i, _i, _i, _p]
+            lib.dryft_argmax_rows.argtypes = [_p, _i, _i, _ll, _p, _p, _p, _p]
+            lib.dryft_sample_rows.argtypes = [_p, _i, _i, _ll, _f, _i, _ull, _p, _p, _i, _p, _p, _p, _p]
+            lib.dryft_gemm_small_m.argtypes = [_p, _i, _p, _p, _i, _i, _i, _i, _i, _p]
+            for name in ("dryft_step_meta", "dryft_step_advance", "dryft_tokens_from_state", "dryft_embed",
+                         "dryft_rmsnorm", "dryft_residual_add", "dryft_silu_mul", "dryft_qk_norm_rope_store",
+                         "dryft_gemm_nt_f32", "dryft_argmax_rows", "dryft_sample_rows", "dryft_gemm_small_m"):
+                getattr(lib, name).restype = _i
+            _core = lib
+        return _core
+
+
+def attention_rows_lib(head_dim: int, group: int, page: int) -> ctypes.CDLL:
+    """The row-wise (decode / 32-bit) attention kernel compiled for these sizes."""
+    if head_dim <= 0 or head_dim % 16:
+        raise KernelError(f"attention kernels take head sizes in steps of 16, got head_dim={head_dim}")
+    if head_dim > 256:
+        raise KernelError(f"attention kernels take head sizes up to 256, got head_dim={head_dim}")
+    if group < 1 or group > 16:
+        raise KernelError(f"attention kernels take 1..16 query heads per kv head, got {group}")
+    key = ("rows", head_dim, group, page)
+    with _lock:
+        lib = _variants.get(key)
+        if lib is None:
+            path = build.build_library("attn_rows", ("attn_rows.cu",),
+                                       {"DRYFT_HEAD_DIM": head_dim, "DRYFT_GROUP": group, "DRYFT_PAGE": page})
+            lib = _load(path)
+            lib.dryft_attn_rows.argtypes = [_i, _p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _f, _i, _p]
+            lib.dryft_attn_rows.restype = _i
+            if (lib.dryft_attn_rows_head_dim(), lib.dryft_attn_rows_group(), lib.dryft_attn_rows_page()) != (head_dim, group, page):
+                raise KernelError(f"{path} was compiled for other sizes")
+            _variants[key] = lib
+        return lib
+
+
+def attention_prefill_lib(head_dim: int, group: int, page: int) -> ctypes.CDLL:
+    """The tensor-core prefill attention kernel (bfloat16) compiled for these sizes."""
+    if head_dim <= 0 or head_dim % 16 or head_dim > 256:
+        raise KernelError(f"prefill attention takes head sizes 16..256 in steps of 16, got head_dim={head_dim}")
+    key = ("prefill", head_dim, group, page)
+    with _lock:
+        lib = _variants.get(key)
+        if lib is None:
+            path = build.build_library("attn_prefill", ("attn_prefill.cu",),
+                                       {"DRYFT_HEAD_DIM": head_dim, "DRYFT_GROUP": group, "DRYFT_PAGE": page})
+            lib = _load(path)
+            lib.dryft_attn_prefill.argtypes = [_p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _f, _i, _p]
+            lib.dryft_attn_prefill.restype = _i
+            _variants[key] = lib
+        return lib
+
+
+# ----------------------------------------------------------------------------- argument checks
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, shape=None) -> torch.Tensor:
+    if not isinstance(t, torch.Tensor):
+        raise KernelError(f"{name}: expected a tensor, got {type(t).__name__}")
+    if t.device.type != "cuda":
+        raise KernelError(f"{name}: is on {t.device}; dryft_b200 kernels run on a CUDA device only")
+    if not t.is_contiguous():
+        raise KernelError(f"{name}: must be contiguous (shape {tuple(t.shape)}, strides {t.stride()})")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name}: expected {dtype}, got {t.dtype}")
+    if shape is not None:
+        if len(shape) != t.dim() or any(s is not None and s != d for s, d in zip(shape, t.shape)):
+            raise KernelError(f"{name}: expected shape {tuple(shape)}, got {tuple(t.shape)}")
+    return t
+
+
+def _act(t: torch.Tensor, name: str) -> int:
+    """1 for bfloat16, 0 for float32; anything else is refused."""
+    if t.dtype == torch.bfloat16:
+        return 1
+    if t.dtype == torch.float32:
+        return 0
+    raise KernelError(f"{name}: activations are float32 or bfloat16, got {t.dtype}")
+
+
+def _ok(rc: int, what: str) -> None:
+    if rc == 0:
+        return
+    if rc == UNSUPPORTED:
+        raise KernelError(f"{what}: sizes not supported by this kernel")
+    raise KernelError(f"{what}: CUDA error {rc} at launch")
+
+
+# ----------------------------------------------------------------------------- step metadata
+def step_meta(cu_q, seq_slot, seq_len, tok_slot, tok_pos, n_tokens: int, n_seqs: int) -> None:
+    for t, n in ((cu_q, "cu_q"), (seq_slot, "seq_slot"), (seq_len, "seq_len"), (tok_slot, "tok_slot"), (tok_pos, "tok_pos")):
+        _need(t, n, torch.int32)
+    if cu_q.numel() < n_seqs + 1 or seq_slot.numel() < n_seqs or tok_slot.numel() < n_tokens or tok_pos.numel() < n_tokens:
+        raise KernelError("step_meta: index arrays shorter than the batch")
+    _ok(core().dryft_step_meta(_ptr(cu_q), _ptr(seq_slot), _ptr(seq_len), n_tokens, n_seqs, _ptr(tok_slot), _ptr(tok_pos),
+                               _stream()), "step_meta")
+
+
+def step_advance(cu_q, seq_slot, seq_len, n_seqs: int) -> None:
+    for t, n in ((cu_q, "cu_q"), (seq_slot, "seq_slot"), (seq_len, "seq_len")):
+        _need(t, n, torch.int32)
+    _ok(core().dryft_step_advance(_ptr(cu_q), _ptr(seq_slot), _ptr(seq_len), n_seqs, _stream()), "step_advance")
+
+
+def tokens_from_state(seq_slot, last_token, tokens, n_seqs: int) -> None:
+    for t, n in ((seq_slot, "seq_slot"), (last_token, "last_token"), (tokens, "tokens")):
+        _need(t, n, torch.int32)
+    _ok(core().dryft_tokens_from_state(_ptr(seq_slot), _ptr(last_token), _ptr(tokens), n_seqs, _stream()), "tokens_from_state")
+
+
+# ----------------------------------------------------------------------------- elementwise
+def embed(tokens, table, out, err=None) -> None:
+    _need(tokens, "tokens", torch.int32)
+    _need(table, "embedding table")
+    n = out.shape[0]
+    _need(out, "embedding output", table.dtype, (n, table.shape[1]))
+    if tokens.numel() < n:
+        raise KernelError("embed: fewer tokens than output rows")
+    if err is not None:
+        _need(err, "err", torch.int32)
+    _ok(core().dryft_embed(_act(table, "embedding table"), _ptr(tokens), _ptr(table), _ptr(out), n, table.shape[1],
+                           table.shape[0], _ptr(err), _stream()), "embed")
+
+
+def rmsnorm(x, weight, eps: float, out, delta=None, rows=None, x_out=None) -> None:
+    """``out[r] = norm(x[src] (+ delta[src])) * weight`` with ``src = rows[r]`` if rows is given;
+    ``x_out[src]`` receives the summed row when given (may alias ``x``)."""
+    hidden = x.shape[-1]
+    _need(x, "x")
+    _need(weight, "norm weight", torch.float32, (hidden,))
+    n_rows = out.shape[0]
+    _need(out, "norm output", x.dtype, (n_rows, hidden))
+    if delta is not None:
+        _need(delta, "delta", x.dtype, tuple(x.shape))
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        if rows.numel() < n_rows:
+            raise KernelError("rmsnorm: fewer row indices than output rows")
+    elif x.shape[0] < n_rows:
+        raise KernelError("rmsnorm: input has fewer rows than the output")
+    if x_out is not None:
+        _need(x_out, "x_out", x.dtype, tuple(x.shape))
+    _ok(core().dryft_rmsnorm(_act(x, "x"), _ptr(x), _ptr(delta), _ptr(weight), _ptr(rows), _ptr(x_out), _ptr(out), n_rows,
+                             hidden, float(eps), _stream()), f"rmsnorm (width {hidden})")
+
+
+def residual_add(x, delta) -> None:
+    _need(x, "x")
+    _need(delta, "delta", x.dtype, tuple(x.shape))
+    _ok(core().dryft_residual_add(_act(x, "x"), _ptr(x), _ptr(delta), x.numel(), _stream()), "residual_add")
+
+
+def silu_mul(gate_up, out) -> None:
+    rows, two_i = gate_up.shape
+    _need(gate_up, "gate_up")
+    if two_i % 2:
+        raise KernelError(f"silu_mul: fused gate|up width must be even, got {two_i}")
+    _need(out, "silu_mul output", gate_up.dtype, (rows, two_i // 2))
+    _ok(core().dryft_silu_mul(_act(gate_up, "gate_up"), _ptr(gate_up), _ptr(out), rows, two_i // 2, _stream()), "silu_mul")
+
+
+# ----------------------------------------------------------------------------- rope + cache write
+def qk_norm_rope_store(qkv, q_norm_w, k_norm_w, inv_freq, tok_slot, tok_pos, q_out, k_pages, v_pages, page_table,
+                       n_heads: int, n_kv_heads: int, head_dim: int, rotary_dim: int, eps: float, write_kv: bool = True) -> None:
+    n = qkv.shape[0]
+    width = (n_heads + (2 * n_kv_heads if write_kv else 0)) * head_dim
+    _need(qkv, "qkv", None, (n, width))
+    is_bf16 = _act(qkv, "qkv")
+    has_norm = q_norm_w is not None
+    if has_norm:
+        _need(q_norm_w, "q_norm weight", torch.float32, (head_dim,))
+        _need(k_norm_w, "k_norm weight", torch.float32, (head_dim,))
+    if rotary_dim:
+        _need(inv_freq, "inv_freq", torch.float32, (rotary_dim // 2,))
+    _need(tok_slot, "tok_slot", torch.int32)
+    _need(tok_pos, "tok_pos", torch.int32)
+    if tok_slot.numel() < n or tok_pos.numel() < n:
+        raise KernelError("qk_norm_rope_store: token index arrays shorter than the batch")
+    _need(q_out, "q_out", qkv.dtype, (n, n_heads, head_dim))
+    page_size, max_pages = 0, 0
+    if write_kv:
+        _need(k_pages, "k_pages", qkv.dtype, (None, n_kv_heads, None, head_dim))
+        _need(v_pages, "v_pages", qkv.dtype, tuple(k_pages.shape))
+        _need(page_table, "page_table", torch.int32)
+        page_size, max_pages = k_pages.shape[2], page_table.shape[1]
+    _ok(core().dryft_qk_norm_rope_store(is_bf16, _ptr(qkv), width, _ptr(q_norm_w), _ptr(k_norm_w), _ptr(inv_freq),
+                                        _ptr(tok_slot), _ptr(tok_pos), _ptr(q_out), _ptr(k_pages if write_kv else None),
+                                        _ptr(v_pages if write_kv else None), _ptr(page_table if write_kv else None),
+                                        max_pages, n, n_heads, n_kv_heads, head_dim, rotary_dim, page_size, float(eps),
+                                        int(has_norm), int(write_kv), _stream()), "qk_norm_rope_store")
+
+
+# ----------------------------------------------------------------------------- attention
+def attn_rows(q, k_pages, v_pages, page_table, tok_slot, tok_pos, out, scale: float, window: Optional[int],
+              n_splits: int = 1, part_o=None, part_ml=None) -> None:
+    n, n_heads, head_dim = q.shape
+    is_bf16 = _act(q, "q")
+    _need(q, "q")
+    n_kv = k_pages.shape[1]
+    page = k_pages.shape[2]
+    _need(k_pages, "k_pages", q.dtype, (None, n_kv, page, head_dim))
+    _need(v_pages, "v_pages", q.dtype, tuple(k_pages.shape))
+    _need(page_table, "page_table", torch.int32)
+    _need(tok_slot, "tok_slot", torch.int32)
+    _need(tok_pos, "tok_pos", torch.int32)
+    if tok_slot.numel() < n or tok_pos.numel() < n:
+        raise KernelError("attn_rows: token index arrays shorter than the batch")
+    _need(out, "attention output", q.dtype, (n, n_heads * head_dim))
+    if n_heads % n_kv:
+        raise KernelError(f"attn_rows: {n_heads} query heads are not a multiple of {n_kv} kv heads")
+    if n_splits > 1:
+        _need(part_o, "part_o", torch.float32)
+        _need(part_ml, "part_ml", torch.float32)
+        if part_o.numel() < n * n_heads * n_splits * head_dim or part_ml.numel() < n * n_heads * n_splits * 2:
+            raise KernelError("attn_rows: partial buffers too small for the split count")
+    lib = attention_rows_lib(head_dim, n_heads // n_kv, page)
+    _ok(lib.dryft_attn_rows(is_bf16, _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(page_table), page_table.shape[1],
+                            _ptr(tok_slot), _ptr(tok_pos), _ptr(out), _ptr(part_o), _ptr(part_ml), n, n_kv, n_splits,
+                            float(scale), int(window or 0), _stream()), f"attn_rows (head_dim {head_dim})")
+
+
+def attn_prefill(q, k_pages, v_pages, page_table, tile_tok0, tile_rows, tok_slot, tok_pos, out, n_tiles: int,
+                 scale: float, window: Optional[int]) -> None:
+    """Causal grouped-query attention of packed prompts over the paged cache (bfloat16, tensor cores).
+    Tile ``t`` covers the ``tile_rows[t]`` query tokens from packed index ``tile_tok0[t]`` on, all of one
+    sequence; their slot and positions are read from ``tok_slot`` / ``tok_pos``."""
+    n, n_heads, head_dim = q.shape
+    _need(q, "q", torch.bfloat16)
+    n_kv = k_pages.shape[1]
+    page = k_pages.shape[2]
+    _need(k_pages, "k_pages", torch.bfloat16, (None, n_kv, page, head_dim))
+    _need(v_pages, "v_pages", torch.bfloat16, tuple(k_pages.shape))
+    for t, nm in ((page_table, "page_table"), (tile_tok0, "tile_tok0"), (tile_rows, "tile_rows"),
+                  (tok_slot, "tok_slot"), (tok_pos, "tok_pos")):
+        _need(t, nm, torch.int32)
+    if tile_tok0.numel() < n_tiles or tile_rows.numel() < n_tiles:
+        raise KernelError("attn_prefill: tile arrays shorter than the tile count")
+    _need(out, "attention output", torch.bfloat16, (n, n_heads * head_dim))
+    if n_heads % n_kv:
+        raise KernelError(f"attn_prefill: {n_heads} query heads are not a multiple of {n_kv} kv heads")
+    lib = attention_prefill_lib(head_dim, n_heads // n_kv, page)
+    _ok(lib.dryft_attn_prefill(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(page_table), page_table.shape[1],
+                               _ptr(tile_tok0), _ptr(tile_rows), _ptr(tok_slot), _ptr(tok_pos), _ptr(out), n_tiles,
+                               n_heads, n_kv, float(scale), int(window or 0), _stream()),
+        f"attn_prefill (head_dim {head_dim})")
+
+
+# ----------------------------------------------------------------------------- matrix products
+def gemm_nt_f32(a, w, out) -> None:
+    """``out[M,N] = a[M,K] @ w[N,K].T`` in true 32-bit."""
+    m, k = a.shape
+    n = w.shape[0]
+    _need(a, "a", torch.float32)
+    _need(w, "w", torch.float32, (n, k))
+    _need(out, "out", torch.float32, (m, n))
+    _ok(core().dryft_gemm_nt_f32(_ptr(a), k, _ptr(w), _ptr(out), n, m, n, k, _stream()), "gemm_nt_f32")
+
+
+def gemm_small_m(a, w, out) -> None:
+    """``out[M,N] = a[M,K] @ w[N,K].T`` for a handful of rows (decode): bfloat16 operands, 32-bit
+    accumulation, ``out`` bfloat16 or float32.  Every weight byte is read once."""
+    m, k = a.shape
+    n = w.shape[0]
+    _need(a, "a", torch.bfloat16)
+    _need(w, "w", torch.bfloat16, (n, k))
+    _need(out, "out", None, (m, n))
+    if out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError(f"gemm_small_m: output must be bfloat16 or float32, got {out.dtype}")
+    _ok(core().dryft_gemm_small_m(_ptr(a), k, _ptr(w), _ptr(out), n, int(out.dtype == torch.float32), m, n, k, _stream()),
+        f"gemm_small_m (M={m}, N={n}, K={k})")
+
+
+# ----------------------------------------------------------------------------- token choice
+def argmax_rows(logits, out, row_slot=None, last_token=None) -> None:
+    rows, vocab = logits.shape
+    _need(logits, "logits", torch.float32)
+    _need(out, "chosen tokens", torch.int32)
+    if out.numel() < rows:
+        raise KernelError("argmax_rows: output shorter than the rows")
+    if row_slot is not None:
+        _need(row_slot, "row_slot", torch.int32)
+        _need(last_token, "last_token", torch.int32)
+    _ok(core().dryft_argmax_rows(_ptr(logits), rows, vocab, vocab, _ptr(out), _ptr(row_slot), _ptr(last_token), _stream()),
+        "argmax_rows")
+
+
+def sample_rows(logits, temperature: float, top_k: int, seed: int, row_seq, row_step, out, row_slot=None, last_token=None,
+                step_base: int = 0) -> None:
+    """Row r draws with uniform(seed, row_seq[r] (or r), step_base + row_step[r] (or 0))."""
+    rows, vocab = logits.shape
+    _need(logits, "logits", torch.float32)
+    _need(out, "chosen tokens", torch.int32)
+    if not temperature > 0.0:
+        raise KernelError("sample_rows: temperature must be positive (use argmax_rows for greedy)")
+    for t, nm in ((row_seq, "row_seq"), (row_step, "row_step")):
+        if t is None:
+            continue
+        _need(t, nm, torch.int32)
+        if t.numel() < rows:
+            raise KernelError(f"sample_rows: {nm} shorter than the rows")
+    if row_slot is not None:
+        _need(row_slot, "row_slot", torch.int32)
+        _need(last_token, "last_token", torch.int32)
+    _ok(core().dryft_sample_rows(_ptr(logits), rows, vocab, vocab, float(temperature), int(top_k), int(seed) & (2**64 - 1),
+                                 _ptr(row_seq), _ptr(row_step), int(step_base), _ptr(out), _ptr(row_slot), _ptr(last_token),
+                                 _stream()), "sample_rows")

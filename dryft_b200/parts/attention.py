@@ -1,0 +1,116 @@
+"""Grouped-query attention over the paged cache, the mixer of every Qwen3 layer.
+
+Per step (``engine/dryft_qwen3/model.py:153-179,237-258``):
+  ``qkv = h @ W_qkv.T`` (rows q; k; v fused, ``weights.py:93-96``) -> per-head RMSNorm of q and k
+  (before RoPE, ``model.py:165-166``) -> rotate-half RoPE at each token's own position -> K and V
+  written into the cache at that position (``model.py:170-171,249-250``) -> attention of every query
+  token over keys ``0..its position`` of its own sequence (``model.py:235``), q head ``h`` reading kv
+  head ``h // G`` -> ``@ W_o.T``.
+
+The three middle stages are one kernel (``csrc/rope_kv.cu``); attention is ``csrc/attn_prefill.cu``
+(bfloat16 prompts, tensor cores) or ``csrc/attn_rows.cu`` (decode, and everything in 32-bit).
+Every size and constant is a parameter: head counts, head size, scale, eps, window, rotary part.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Dict, Mapping, Optional
+
+import torch
+
+from ..cache.store import CacheEntry, KVNeed, StateNeed
+from ..config.spec import PartSpec
+from ..ops import kernels as K
+from .base import NORMS, POSITIONS, Runtime, StepContext, TensorInfo, register_mixer
+from .linear import linear
+
+PREFILL_TILE = 64  # query rows per block of the tensor-core prefill kernel
+
+
+@register_mixer("attention")
+class Attention:
+    @staticmethod
+    def tensors(params: Mapping, prefix: str) -> Dict[str, TensorInfo]:
+        h, nh, nkv, d = params["hidden_size"], params["num_heads"], params["num_kv_heads"], params["head_dim"]
+        t = {
+            prefix + "q_proj.weight": TensorInfo((nh * d, h), "matrix"),
+            prefix + "k_proj.weight": TensorInfo((nkv * d, h), "matrix"),
+            prefix + "v_proj.weight": TensorInfo((nkv * d, h), "matrix"),
+            prefix + "o_proj.weight": TensorInfo((h, nh * d), "matrix"),
+        }
+        qk = params.get("qk_norm")
+        if qk is not None:
+            t.update(NORMS.get(qk.kind).tensors(qk.params, prefix + "q_norm."))
+            t.update(NORMS.get(qk.kind).tensors(qk.params, prefix + "k_norm."))
+        return t
+
+    def __init__(self, params: Mapping, prefix: str, weights, rt: Runtime):
+        self.rt = rt
+        self.hidden = int(params["hidden_size"])
+        self.n_heads = int(params["num_heads"])
+        self.n_kv = int(params["num_kv_heads"])
+        self.head_dim = int(params["head_dim"])
+        self.scale = float(params["scale"])
+        self.window: Optional[int] = params.get("window")
+        if self.n_heads % self.n_kv:
+            raise ValueError(f"attention: {self.n_heads} heads are not a multiple of {self.n_kv} kv heads")
+        self.group = self.n_heads // self.n_kv
+        self.q_dim = self.n_heads * self.head_dim
+        self.kv_dim = self.n_kv * self.head_dim
+        names = [prefix + f"{p}_proj.weight" for p in ("q", "k", "v")]
+        self.w_qkv = weights.load_fused(names, [self.q_dim, self.kv_dim, self.kv_dim], self.hidden)
+        self.w_o = weights.load(prefix + "o_proj.weight", "matrix")
+        qk: Optional[PartSpec] = params.get("qk_norm")
+        self.qk_eps = 0.0
+        self.q_norm_w = self.k_norm_w = None
+        if qk is not None:
+            if qk.kind != "rmsnorm" or int(qk["size"]) != self.head_dim:
+                raise ValueError("attention: the per-head q/k norm must be an rmsnorm over head_dim")
+            self.qk_eps = float(qk["eps"])
+            self.q_norm_w = weights.load(prefix + "q_norm.weight", "vector")
+            self.k_norm_w = weights.load(prefix + "k_norm.weight", "vector")
+        pos: PartSpec = params.get("position") or PartSpec("none")
+        self.position = POSITIONS.get(pos.kind)(pos.params, self.head_dim, rt)
+        # build (or find) the kernels this head shape needs now, not at the first step
+        K.attention_rows_lib(self.head_dim, self.group, rt.page_size)
+        self.use_prefill_kernel = rt.is_bf16
+        if self.use_prefill_kernel:
+            K.attention_prefill_lib(self.head_dim, self.group, rt.page_size)
+
+    def kv_need(self) -> Optional[KVNeed]:
+        return KVNeed(self.n_kv, self.head_dim, self.window)
+
+    def state_need(self) -> Optional[StateNeed]:
+        return None
+
+    def _n_splits(self, n_rows: int) -> int:
+        """Split the keys of each row over enough blocks to fill the device (the reference aims at
+        two programs per SM, ``kernels/attn_decode.py:143-149``)."""
+        want = math.ceil(2 * self.rt.sm_count / max(1, n_rows * self.n_kv))
+        return max(1, min(32, want))
+
+    def forward(self, h: torch.Tensor, ctx: StepContext, cache: CacheEntry, state, owns_cache: bool = True) -> torch.Tensor:
+        n = h.shape[0]
+        dev = h.device
+        if owns_cache:
+            qkv = linear(h, self.w_qkv, self.rt)
+        else:  # a run step that reads another step's cache projects queries only
+            qkv = linear(h, self.w_qkv[: self.q_dim], self.rt)
+        q = torch.empty((n, self.n_heads, self.head_dim), dtype=h.dtype, device=dev)
+        K.qk_norm_rope_store(qkv, self.q_norm_w, self.k_norm_w, self.position.inv_freq, ctx.tok_slot, ctx.tok_pos, q,
+                             cache.k, cache.v, cache.page_table, self.n_heads, self.n_kv, self.head_dim,
+                             self.position.rotary_dim, self.qk_eps, write_kv=owns_cache)
+        o = torch.empty((n, self.q_dim), dtype=h.dtype, device=dev)
+        if self.use_prefill_kernel and not ctx.decode and ctx.n_tiles > 0:
+            K.attn_prefill(q, cache.k, cache.v, cache.page_table, ctx.tile_tok0, ctx.tile_rows, ctx.tok_slot, ctx.tok_pos,
+                           o, ctx.n_tiles, self.scale, self.window)
+        else:
+            s = self._n_splits(n)
+            part_o = part_ml = None
+            if s > 1:
+                part_o = torch.empty((n, self.n_heads, s, self.head_dim), dtype=torch.float32, device=dev)
+                part_ml = torch.empty((n, self.n_heads, s, 2), dtype=torch.float32, device=dev)
+            K.attn_rows(q, cache.k, cache.v, cache.page_table, ctx.tok_slot, ctx.tok_pos, o, self.scale, self.window,
+                        s, part_o, part_ml)
+        return linear(o, self.w_o, self.rt)

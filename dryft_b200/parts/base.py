@@ -1,0 +1,115 @@
+"""What every part of a layer has in common: the registries that map a ``PartSpec.kind`` to a class,
+the description of the tensors a part reads from the checkpoint, and the context a step hands to
+the parts.  No part knows which model it is in; it sees its own parameters, its own tensors, the
+step's token metadata and (for a mixer) its own cache entry and state.
+
+Interfaces
+----------
+norm        ``tensors(params, prefix)``; ``__init__(params, prefix, weights, rt)``;
+            ``forward(x, out=None)``; ``add_forward(x, delta, rows=None)`` -> normed rows, with
+            ``x += delta`` written back (fused residual add, ``kernels/rmsnorm.py:21-39``).
+position    ``__init__(params, head_dim, rt)``; gives ``rotary_dim`` and ``inv_freq`` to the mixer.
+mixer       ``tensors``; ``__init__``; ``kv_need()`` / ``state_need()``;
+            ``forward(h, ctx, cache, state, owns_cache)`` -> ``[tokens, hidden]`` (not yet added).
+ffn         ``tensors``; ``__init__``; ``forward(h, ctx)`` -> ``[tokens, hidden]``.
+block       ``__init__(layer_spec, norm_mixer, mixer, norm_ffn, ffn)``;
+            ``forward(x, delta, ctx, cache, state, owns_cache)`` -> ``(x, delta)``: the residual stream and the
+            not-yet-added output of the block's last part, so the next norm can fuse the add.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, Mapping, NamedTuple, Optional, Tuple
+
+import torch
+
+from ..config.spec import PartSpec
+
+
+class TensorInfo(NamedTuple):
+    """One checkpoint tensor a part expects.  ``kind``: "matrix" (a product's weight), "vector"
+    (norm weights and other 1-D tensors, kept in 32-bit on the device) or "table" (embedding)."""
+
+    shape: Tuple[int, ...]
+    kind: str
+    optional: bool = False
+
+
+@dataclass
+class Runtime:
+    """Where and how the parts compute."""
+
+    dtype: torch.dtype           # activation dtype: torch.float32 or torch.bfloat16
+    device: torch.device
+    page_size: int = 64
+    sm_count: int = 148
+    small_m_max: int = 16        # decode rows up to which the weight-streaming product is used
+    ffn_chunk_rows: int = 16384  # rows of the feed-forward processed at once (bounds [rows, 2I])
+
+    @property
+    def is_bf16(self) -> bool:
+        return self.dtype == torch.bfloat16
+
+
+@dataclass
+class StepContext:
+    """Token metadata of one step, on the device unless noted."""
+
+    n_tokens: int                 # activation rows (padding rows included)
+    n_seqs: int
+    tokens: torch.Tensor          # int32 [n_tokens]
+    cu_q: torch.Tensor            # int32 [n_seqs + 1]: sequence b's tokens are cu_q[b]..cu_q[b+1]-1
+    seq_slot: torch.Tensor        # int32 [n_seqs]: cache slot, -1 for a padding sequence
+    tok_slot: torch.Tensor        # int32 [n_tokens]
+    tok_pos: torch.Tensor         # int32 [n_tokens]: absolute position of each token
+    decode: bool                  # host: every sequence brings exactly one token
+    tile_tok0: Optional[torch.Tensor] = None   # int32 [n_tiles]: first packed token of a query tile
+    tile_rows: Optional[torch.Tensor] = None   # int32 [n_tiles]: tokens in the tile (<= tile_size)
+    n_tiles: int = 0
+    tile_size: int = 0
+    extras: Dict[str, Any] = field(default_factory=dict)
+
+
+class Registry:
+    def __init__(self, what: str):
+        self.what = what
+        self._classes: Dict[str, Any] = {}
+
+    def register(self, kind: str, cls: Any = None):
+        """``register(kind, cls)`` or ``@register(kind)``."""
+        if cls is None:
+            def deco(c):
+                self._classes[kind] = c
+                return c
+            return deco
+        self._classes[kind] = cls
+        return cls
+
+    def unregister(self, kind: str) -> None:
+        self._classes.pop(kind, None)
+
+    def get(self, kind: str) -> Any:
+        if kind not in self._classes:
+            raise KeyError(f"unknown {self.what} kind {kind!r}; registered: " + ", ".join(sorted(self._classes)))
+        return self._classes[kind]
+
+    def kinds(self):
+        return sorted(self._classes)
+
+
+MIXERS = Registry("mixer")
+FFNS = Registry("feed-forward")
+NORMS = Registry("norm")
+POSITIONS = Registry("position encoding")
+BLOCKS = Registry("block arrangement")
+EMBEDDINGS = Registry("embedding")
+HEADS = Registry("output head")
+
+register_mixer = MIXERS.register
+register_ffn = FFNS.register
+register_norm = NORMS.register
+register_position = POSITIONS.register
+register_block = BLOCKS.register
+register_embedding = EMBEDDINGS.register
+register_head = HEADS.register

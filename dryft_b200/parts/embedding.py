@@ -1,0 +1,67 @@
+"""Token embedding ``x = embed[ids]`` (``engine/dryft_qwen3/model.py:132,226``) and the output head
+``logits = h @ W_head.T`` with ``W_head`` the embedding table itself when tied
+(``engine/dryft_qwen3/weights.py:47-49``).  Unlike the reference, an untied ``lm_head.weight`` is
+served (``weights.py:84-85`` refuses it), and logits leave the product's 32-bit accumulator
+unrounded.
+"""
+
+from __future__ import annotations
+
+from typing import Dict, Mapping, Optional
+
+import torch
+
+from ..ops import kernels as K
+from .base import Runtime, TensorInfo, register_embedding, register_head
+from .linear import linear
+
+
+@register_embedding("embedding")
+class Embedding:
+    @staticmethod
+    def tensors(params: Mapping, prefix: str) -> Dict[str, TensorInfo]:
+        return {prefix + "weight": TensorInfo((params["vocab_size"], params["hidden_size"]), "table")}
+
+    def __init__(self, params: Mapping, prefix: str, weights, rt: Runtime):
+        self.rt = rt
+        self.vocab = int(params["vocab_size"])
+        self.hidden = int(params["hidden_size"])
+        self.table = weights.load(prefix + "weight", "table")
+        self.err = torch.zeros(1, dtype=torch.int32, device=rt.device)
+
+    def forward(self, tokens: torch.Tensor, n_rows: int) -> torch.Tensor:
+        out = torch.empty((n_rows, self.hidden), dtype=self.table.dtype, device=self.table.device)
+        K.embed(tokens, self.table, out, self.err)
+        # a table the checkpoint stores in 32-bit stays 32-bit; its rows are rounded on the way out
+        return out if out.dtype == self.rt.dtype else out.to(self.rt.dtype)
+
+
+@register_head("lm_head")
+class LMHead:
+    @staticmethod
+    def tensors(params: Mapping, prefix: str) -> Dict[str, TensorInfo]:
+        return {prefix + "weight": TensorInfo((params["vocab_size"], params["hidden_size"]), "matrix",
+                                        optional=bool(params["tied"]))}
+
+    def __init__(self, params: Mapping, prefix: str, weights, rt: Runtime, embedding: Optional[Embedding] = None):
+        self.rt = rt
+        self.vocab = int(params["vocab_size"])
+        self.tied = bool(params["tied"])
+        name = prefix + "weight"
+        if self.tied:
+            if embedding is None:
+                raise ValueError("a tied output head needs the embedding it is tied to")
+            self.weight = embedding.table
+            if weights.has(name):
+                # present although tied: it has to be the same tensor (weights.py:86-87)
+                other = weights.load(name, "matrix")
+                if other.shape != self.weight.shape or not torch.equal(other.to(self.weight.dtype), self.weight):
+                    raise ValueError(f"{name} is present and differs from the embedding table although the "
+                                     "output head is tied to it")
+                del other
+        else:
+            self.weight = weights.load(name, "matrix")
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        """32-bit logits ``[rows, vocab]``."""
+        return linear(h, self.weight, self.rt, out_dtype=torch.float32)

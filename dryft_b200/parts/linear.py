@@ -1,0 +1,49 @@
+"""``y = x @ W.T`` for the weights of the parts (all ``[out, in]``, no bias — ``OPTIMIZATION_GUIDE.md:117``;
+``engine/dryft_qwen3/config.py:138``).
+
+Which product runs:
+  * 32-bit activations (the 32-bit path): the hand-written CUDA-core product, true fp32;
+  * bfloat16, few rows (decode): the hand-written weight-streaming tensor-core product;
+  * bfloat16, many rows (prefill): cuBLAS through ``torch.mm``, 32-bit accumulation — the library
+    product the reference itself uses (``F.linear``, ``engine/dryft_qwen3/model.py:153,179,180``);
+  * bfloat16 activations with a weight the checkpoint stores in 32-bit: the weight stays 32-bit,
+    the activations are widened, the 32-bit product runs and its result is rounded once.
+"""
+
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from ..ops import kernels as K
+from .base import Runtime
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, rt: Runtime, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    out_dtype = out_dtype or x.dtype
+    m, k = x.shape
+    n = w.shape[0]
+    if w.shape[1] != k:
+        raise ValueError(f"linear: activations have width {k}, weight is {tuple(w.shape)}")
+    if x.dtype == torch.float32:
+        if w.dtype != torch.float32:
+            raise ValueError(f"linear: 32-bit activations need a 32-bit weight, got {w.dtype}")
+        out = torch.empty((m, n), dtype=torch.float32, device=x.device)
+        K.gemm_nt_f32(x, w, out)
+        return out if out_dtype == torch.float32 else out.to(out_dtype)
+    if x.dtype != torch.bfloat16:
+        raise ValueError(f"linear: activations are float32 or bfloat16, got {x.dtype}")
+    if w.dtype == torch.float32:
+        out = torch.empty((m, n), dtype=torch.float32, device=x.device)
+        K.gemm_nt_f32(x.to(torch.float32), w, out)
+        return out if out_dtype == torch.float32 else out.to(out_dtype)
+    if w.dtype != torch.bfloat16:
+        raise ValueError(f"linear: weight dtype {w.dtype} is not supported")
+    if m <= rt.small_m_max and k % 8 == 0:
+        out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+        K.gemm_small_m(x, w, out)
+        return out
+    if out_dtype == torch.bfloat16:
+        return torch.mm(x, w.t())
+    return torch.mm(x, w.t(), out_dtype=out_dtype)
