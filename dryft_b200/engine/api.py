@@ -95,7 +95,7 @@ class Engine:
         props = torch.cuda.get_device_properties(dev)
         self.rt = Runtime(dtype=dtype, device=dev, page_size=opts.page_size, sm_count=props.multi_processor_count,
                           small_m_max=opts.small_m_max)
-        with torch.cuda.device(dev), torch.inference_mode():
+        with torch.cuda.device(dev), torch.no_grad():
             self.model = DecoderModel(spec, source, self.rt)
             self.max_seq_len = opts.max_seq_len or min(spec.max_positions, 8192)
             self.max_batch = opts.max_batch

@@ -1,0 +1,379 @@
+"""Each CUDA kernel alone against a plain PyTorch 32-bit reference of the same operation, at sizes
+other than the tiny models': widths that are no power of two, odd row counts, head sizes 16..256,
+several group sizes, vocabularies that are prime.  Outputs are surrounded by canary values where a
+kernel could write out of its place (the reference's own self-tests check "nothing else in the cache
+was touched", ``engine/dryft_qwen3/kernels/rope_qknorm.py:199-202,225-227``)."""
+
+import math
+
+import pytest
+import torch
+
+import plain_qwen3 as P
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda"
+
+
+def K():
+    from dryft_b200.ops import kernels
+
+    return kernels
+
+
+def _r(x, dtype):
+    return x.to(dtype).to(torch.float32)
+
+
+def _tol(dtype):
+    # one bf16 rounding of the result (2^-8 relative) plus accumulation-order noise; fp32: a few ulps
+    return (2e-2, 2e-2) if dtype == torch.bfloat16 else (2e-5, 2e-5)
+
+
+# ------------------------------------------------------------------------------------ metadata
+def test_step_meta_and_advance():
+    k = K()
+    cu = torch.tensor([0, 3, 4, 9], dtype=torch.int32, device=DEV)
+    slot = torch.tensor([5, -1, 2], dtype=torch.int32, device=DEV)
+    seq_len = torch.tensor([0, 0, 7, 0, 0, 100, 0, 0], dtype=torch.int32, device=DEV)
+    n = 12  # 3 padding tokens beyond cu[-1]
+    ts = torch.full((n,), 77, dtype=torch.int32, device=DEV)
+    tp = torch.full((n,), 77, dtype=torch.int32, device=DEV)
+    k.step_meta(cu, slot, seq_len, ts, tp, n, 3)
+    assert ts.tolist() == [5, 5, 5, -1, 2, 2, 2, 2, 2, -1, -1, -1]
+    assert tp.tolist() == [100, 101, 102, 0, 7, 8, 9, 10, 11, 0, 0, 0]
+    k.step_advance(cu, slot, seq_len, 3)
+    assert seq_len.tolist() == [0, 0, 12, 0, 0, 103, 0, 0]
+
+
+# ------------------------------------------------------------------------------------ embedding
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hidden", [80, 2560, 36])
+def test_embed(dtype, hidden):
+    k = K()
+    vocab = 331
+    table = torch.randn(vocab, hidden, device=DEV).to(dtype)
+    toks = torch.tensor([0, 330, 17, 17, 5], dtype=torch.int32, device=DEV)
+    out = torch.full((5, hidden), 9.0, device=DEV).to(dtype)
+    err = torch.zeros(1, dtype=torch.int32, device=DEV)
+    k.embed(toks, table, out, err)
+    assert torch.equal(out, table[toks.long()])
+    assert err.item() == 0
+    bad = torch.tensor([3, vocab, -1], dtype=torch.int32, device=DEV)
+    out3 = torch.full((3, hidden), 9.0, device=DEV).to(dtype)
+    k.embed(bad, table, out3, err)
+    assert err.item() == 1 and torch.equal(out3[0], table[3]) and out3[1:].abs().max().item() == 0
+
+
+# ------------------------------------------------------------------------------------ norms
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,hidden,eps", [(1, 80, 1e-5), (7, 2560, 1e-6), (33, 200, 3e-6), (3, 13000, 1e-6)])
+def test_rmsnorm_plain_add_gather(dtype, rows, hidden, eps):
+    k = K()
+    x = (torch.randn(rows, hidden, device=DEV) * 3).to(dtype)
+    d = torch.randn(rows, hidden, device=DEV).to(dtype)
+    w = (1 + 0.1 * torch.randn(hidden, device=DEV)).to(dtype).float()
+    rt, at = _tol(dtype)
+    # plain
+    out = torch.empty_like(x)
+    k.rmsnorm(x, w, eps, out)
+    ref = P.rmsnorm(x.cpu(), w.cpu(), eps)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=rt, atol=at)
+    # fused residual add: x updated in place, exactly the rounded 32-bit sum
+    x2 = x.clone()
+    k.rmsnorm(x2, w, eps, out, delta=d, x_out=x2)
+    s = P.residual_add(x.cpu(), d.cpu())
+    assert torch.equal(x2.cpu(), s)
+    torch.testing.assert_close(out.cpu().float(), P.rmsnorm(s, w.cpu(), eps).float(), rtol=rt, atol=at)
+    # gathered rows, input untouched
+    idx = torch.tensor([rows - 1, 0, rows // 2], dtype=torch.int32, device=DEV)
+    x3 = x.clone()
+    outg = torch.empty(3, hidden, device=DEV, dtype=dtype)
+    k.rmsnorm(x3, w, eps, outg, delta=d, rows=idx)
+    assert torch.equal(x3, x)
+    torch.testing.assert_close(outg.cpu().float(), P.rmsnorm(s[idx.cpu().long()], w.cpu(), eps).float(), rtol=rt, atol=at)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,inter", [(1, 224), (5, 9728), (19, 177)])
+def test_silu_mul(dtype, rows, inter):
+    k = K()
+    gu = (torch.randn(rows, 2 * inter, device=DEV) * 4).to(dtype)
+    out = torch.empty(rows, inter, device=DEV, dtype=dtype)
+    k.silu_mul(gu, out)
+    ref = P.silu_mul(gu[:, :inter].cpu(), gu[:, inter:].cpu())
+    rt, at = _tol(dtype)
+    torch.testing.assert_close(out.cpu().float(), ref.float(), rtol=rt, atol=at)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_residual_add(dtype):
+    k = K()
+    x = torch.randn(7, 333, device=DEV).to(dtype)
+    d = torch.randn(7, 333, device=DEV).to(dtype)
+    ref = P.residual_add(x.cpu(), d.cpu())
+    k.residual_add(x, d)
+    assert torch.equal(x.cpu(), ref)
+
+
+# ------------------------------------------------------------------------------------ matrix products
+@pytest.mark.parametrize("m,n,k_", [(1, 1, 1), (5, 67, 33), (64, 64, 16), (130, 257, 100), (3, 384, 80)])
+def test_gemm_f32(m, n, k_):
+    k = K()
+    a = torch.randn(m, k_, device=DEV)
+    w = torch.randn(n, k_, device=DEV)
+    out = torch.full((m, n), 7.0, device=DEV)
+    k.gemm_nt_f32(a, w, out)
+    ref = (a.double() @ w.double().T).float()
+    torch.testing.assert_close(out, ref, rtol=1e-5, atol=1e-5 * math.sqrt(k_))
+    # a row's result does not depend on the other rows in the batch: bit-identical
+    out1 = torch.empty(1, n, device=DEV)
+    k.gemm_nt_f32(a[m - 1:m].contiguous(), w, out1)
+    assert torch.equal(out1[0], out[m - 1])
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 17, 32, 33, 64])
+@pytest.mark.parametrize("n,k_", [(2560, 2560), (331, 96), (19, 4096), (6144, 1000), (48, 8)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_small_m(m, n, k_, out_dtype):
+    k = K()
+    a = torch.randn(m, k_, device=DEV).to(torch.bfloat16)
+    w = (torch.randn(n, k_, device=DEV) / math.sqrt(k_)).to(torch.bfloat16)
+    out = torch.full((m, n), 5.0, device=DEV, dtype=out_dtype)
+    k.gemm_small_m(a, w, out)
+    ref = a.double() @ w.double().T
+    tol = 1e-2 if out_dtype == torch.bfloat16 else 1e-4
+    torch.testing.assert_close(out.double(), ref, rtol=tol, atol=tol)
+    # independent of the batch: row 0 alone gives the same bits
+    out1 = torch.empty(1, n, device=DEV, dtype=out_dtype)
+    k.gemm_small_m(a[:1].contiguous(), w, out1)
+    assert torch.equal(out1[0], out[0])
+
+
+def test_gemm_small_m_refuses_odd_k():
+    k = K()
+    a = torch.zeros(2, 12, device=DEV, dtype=torch.bfloat16)
+    w = torch.zeros(4, 12, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(k.KernelError):
+        k.gemm_small_m(a, w, torch.empty(2, 4, device=DEV, dtype=torch.bfloat16))
+
+
+# ------------------------------------------------------------------------------------ rope + cache write
+def _paged_cache(n_pages, n_kv, page, d, dtype, fill=0.0):
+    kc = torch.full((n_pages, n_kv, page, d), fill, device=DEV).to(dtype)
+    return kc, kc.clone()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n_heads,n_kv,d,rot,theta,eps", [(4, 2, 16, 16, 1e4, 1e-6), (6, 2, 48, 48, 5e5, 1e-5),
+                                                            (8, 8, 128, 128, 5e6, 1e-6), (3, 1, 64, 32, 1e4, 1e-6)])
+def test_qk_norm_rope_store(dtype, n_heads, n_kv, d, rot, theta, eps):
+    k = K()
+    page, n_pages, max_pages, slots = 64, 9, 4, 3
+    # tokens of two sequences at scattered positions (page boundaries 63/64, a far position)
+    tok_slot = torch.tensor([2, 2, 2, 0, 0, -1], dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor([62, 63, 64, 0, 200, 0], dtype=torch.int32, device=DEV)
+    n = 6
+    pt = torch.zeros(slots, max_pages, dtype=torch.int32, device=DEV)
+    pt[2, 0], pt[2, 1], pt[0, 0], pt[0, 3] = 7, 3, 5, 1
+    width = (n_heads + 2 * n_kv) * d
+    qkv = (torch.randn(n, width, device=DEV) * 2).to(dtype)
+    wq = (1 + 0.1 * torch.randn(d, device=DEV)).to(dtype).float()
+    wk = (1 + 0.1 * torch.randn(d, device=DEV)).to(dtype).float()
+    inv_freq = (1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.int64).float() / rot))).to(DEV)
+    canary = 123.0
+    kc, vc = _paged_cache(n_pages, n_kv, page, d, dtype, canary)
+    q_out = torch.full((n, n_heads, d), canary, device=DEV).to(dtype)
+    k.qk_norm_rope_store(qkv, wq, wk, inv_freq, tok_slot, tok_pos, q_out, kc, vc, pt, n_heads, n_kv, d, rot, eps)
+
+    # plain reference
+    qc = qkv.cpu()
+    q = qc[:, :n_heads * d].view(n, n_heads, d)
+    kk = qc[:, n_heads * d:(n_heads + n_kv) * d].view(n, n_kv, d)
+    vv = qc[:, (n_heads + n_kv) * d:].view(n, n_kv, d)
+    qn = P.rmsnorm(q, wq.cpu(), eps)
+    kn = P.rmsnorm(kk, wk.cpu(), eps)
+    cos, sin = P.rope_cos_sin(tok_pos.cpu(), rot, theta, dtype)
+
+    def rot_part(x):
+        return torch.cat((P.apply_rope(x[..., :rot], cos, sin), x[..., rot:]), dim=-1)
+
+    q_ref, k_ref = rot_part(qn), rot_part(kn)
+    rt, at = _tol(dtype)
+    live = [0, 1, 2, 3, 4]
+    torch.testing.assert_close(q_out[live].cpu().float(), q_ref[live].float(), rtol=rt, atol=at)
+    assert q_out[5].abs().max().item() == 0  # padding token: zero query
+    touched = torch.zeros(n_pages, n_kv, page, dtype=torch.bool)
+    for i in live:
+        s, p = int(tok_slot[i]), int(tok_pos[i])
+        pg = int(pt[s, p // page])
+        torch.testing.assert_close(kc[pg, :, p % page].cpu().float(), k_ref[i].float(), rtol=rt, atol=at)
+        assert torch.equal(vc[pg, :, p % page].cpu(), vv[i])
+        touched[pg, :, p % page] = True
+    # nothing else in the cache was written
+    assert (kc.cpu().float()[~touched] == canary).all() and (vc.cpu().float()[~touched] == canary).all()
+
+
+# ------------------------------------------------------------------------------------ attention
+def _fill_cache(seqs, n_kv, d, page, dtype, n_pages, max_pages, slots, scatter_seed=0):
+    """Put each sequence's keys/values into randomly chosen pages; returns caches, page table."""
+    g = torch.Generator().manual_seed(scatter_seed)
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    kc, vc = _paged_cache(n_pages, n_kv, page, d, dtype, 0.0)
+    pt = torch.zeros(slots, max_pages, dtype=torch.int32, device=DEV)
+    for slot, (kseq, vseq) in seqs.items():
+        L = kseq.shape[0]
+        for lp in range((L + page - 1) // page):
+            pp = perm.pop()
+            pt[slot, lp] = pp
+            n = min(page, L - lp * page)
+            kc[pp, :, :n] = kseq[lp * page:lp * page + n].transpose(0, 1).to(DEV)
+            vc[pp, :, :n] = vseq[lp * page:lp * page + n].transpose(0, 1).to(DEV)
+    return kc, vc, pt
+
+
+def _attn_ref(q, kseq, vseq, pos, scale, window):
+    """q [nH, D] at position pos over keys 0..pos of one sequence (32-bit)."""
+    nH, D = q.shape
+    nKV = kseq.shape[1]
+    G = nH // nKV
+    lo = max(0, pos + 1 - window) if window else 0
+    kf = kseq[lo:pos + 1].float()
+    vf = vseq[lo:pos + 1].float()
+    qf = q.float().view(nKV, G, D)
+    sc = torch.einsum("hgd,nhd->hgn", qf, kf) * scale
+    p = torch.softmax(sc, dim=-1)
+    return torch.einsum("hgn,nhd->hgd", p, vf).reshape(nH * D)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n_heads,n_kv,d", [(4, 2, 16), (6, 2, 48), (8, 2, 128), (5, 5, 64), (16, 1, 32), (2, 1, 256)])
+@pytest.mark.parametrize("window", [None, 70])
+def test_attn_rows(dtype, n_heads, n_kv, d, window):
+    k = K()
+    page = 64
+    lens = {0: 1, 1: 63, 2: 64, 3: 65, 4: 300}
+    seqs = {s: ((torch.randn(L, n_kv, d)).to(dtype), torch.randn(L, n_kv, d).to(dtype)) for s, L in lens.items()}
+    kc, vc, pt = _fill_cache(seqs, n_kv, d, page, dtype, n_pages=16, max_pages=6, slots=6)
+    # rows: the last position of every sequence, a middle position, and a padding row
+    rows = [(0, 0), (1, 62), (2, 63), (3, 64), (4, 299), (4, 150), (-1, 0), (4, 64)]
+    tok_slot = torch.tensor([r[0] for r in rows], dtype=torch.int32, device=DEV)
+    tok_pos = torch.tensor([r[1] for r in rows], dtype=torch.int32, device=DEV)
+    n = len(rows)
+    q = torch.randn(n, n_heads, d).to(dtype)
+    scale = 1.0 / math.sqrt(d)
+    ref = torch.stack([
+        _attn_ref(q[i], seqs[s][0], seqs[s][1], p, scale, window) if s >= 0 else torch.zeros(n_heads * d)
+        for i, (s, p) in enumerate(rows)])
+    rt, at = _tol(dtype)
+    for splits in (1, 3, 8):
+        out = torch.full((n, n_heads * d), 9.0, device=DEV).to(dtype)
+        part_o = torch.empty(n, n_heads, splits, d, device=DEV) if splits > 1 else None
+        part_ml = torch.empty(n, n_heads, splits, 2, device=DEV) if splits > 1 else None
+        k.attn_rows(q.to(DEV), kc, vc, pt, tok_slot, tok_pos, out, scale, window, splits, part_o, part_ml)
+        assert torch.isfinite(out.float()).all()
+        torch.testing.assert_close(out.cpu().float(), ref, rtol=rt, atol=at)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attn_rows_far_key_stands_out(dtype):
+    """One key among hundreds is made to dominate (query and that key scaled so its score stands out);
+    the output must be that key's value, wherever in the cache the key lies — first page, a page
+    boundary, the last position — and whatever the split count."""
+    k = K()
+    n_heads, n_kv, d, page, L = 4, 2, 32, 64, 700
+    scale = 1.0 / math.sqrt(d)
+    for target in (0, 63, 64, 333, 639, 640, 699):
+        kseq = torch.randn(L, n_kv, d) * 0.1
+        vseq = torch.randn(L, n_kv, d)
+        q = torch.randn(1, n_heads, d) * 0.1
+        direction = torch.randn(d)
+        direction /= direction.norm()
+        kseq[target] = direction * 30.0
+        q[0] = direction * 30.0
+        seqs = {1: (kseq.to(dtype), vseq.to(dtype))}
+        kc, vc, pt = _fill_cache(seqs, n_kv, d, page, dtype, n_pages=13, max_pages=12, slots=2, scatter_seed=target)
+        tok_slot = torch.tensor([1], dtype=torch.int32, device=DEV)
+        tok_pos = torch.tensor([L - 1], dtype=torch.int32, device=DEV)
+        for splits in (1, 5):
+            out = torch.empty(1, n_heads * d, device=DEV, dtype=dtype)
+            po = torch.empty(1, n_heads, splits, d, device=DEV) if splits > 1 else None
+            pm = torch.empty(1, n_heads, splits, 2, device=DEV) if splits > 1 else None
+            k.attn_rows(q.to(dtype).to(DEV), kc, vc, pt, tok_slot, tok_pos, out, scale, None, splits, po, pm)
+            want = seqs[1][1][target].float().repeat_interleave(n_heads // n_kv, dim=0).reshape(-1)
+            torch.testing.assert_close(out[0].cpu().float(), want, rtol=2e-2, atol=2e-2)
+
+
+@pytest.mark.parametrize("n_heads,n_kv,d", [(4, 2, 16), (6, 2, 48), (8, 2, 128), (3, 3, 64), (2, 1, 256)])
+@pytest.mark.parametrize("window", [None, 40])
+def test_attn_prefill(n_heads, n_kv, d, window):
+    """Packed prompts of unequal lengths, some continuing an earlier chunk, against plain attention."""
+    k = K()
+    dtype = torch.bfloat16
+    page, tile = 64, 64
+    scale = 1.0 / math.sqrt(d)
+    # (slot, tokens already cached, new tokens of this step)
+    plan = [(3, 0, 1), (0, 0, 130), (5, 100, 77), (1, 64, 64), (2, 0, 63)]
+    seqs = {}
+    for slot, old, new in plan:
+        L = old + new
+        seqs[slot] = (torch.randn(L, n_kv, d).to(dtype), torch.randn(L, n_kv, d).to(dtype))
+    kc, vc, pt = _fill_cache(seqs, n_kv, d, page, dtype, n_pages=20, max_pages=4, slots=6, scatter_seed=3)
+    tok_slot, tok_pos, tiles0, tilesn, qs, refs = [], [], [], [], [], []
+    base = 0
+    for slot, old, new in plan:
+        q = torch.randn(new, n_heads, d).to(dtype)
+        qs.append(q)
+        for i in range(new):
+            tok_slot.append(slot)
+            tok_pos.append(old + i)
+            refs.append(_attn_ref(q[i], seqs[slot][0], seqs[slot][1], old + i, scale, window))
+        for q0 in range(0, new, tile):
+            tiles0.append(base + q0)
+            tilesn.append(min(tile, new - q0))
+        base += new
+    n = base
+    q_all = torch.cat(qs).to(DEV)
+    out = torch.full((n, n_heads * d), 9.0, device=DEV, dtype=dtype)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    k.attn_prefill(q_all, kc, vc, pt, i32(tiles0), i32(tilesn), i32(tok_slot), i32(tok_pos), out, len(tiles0), scale, window)
+    ref = torch.stack(refs)
+    assert torch.isfinite(out.float()).all()
+    torch.testing.assert_close(out.cpu().float(), ref, rtol=2e-2, atol=2e-2)
+
+
+# ------------------------------------------------------------------------------------ token choice
+def test_argmax_rows_ties_and_state():
+    k = K()
+    vocab = 1543
+    lg = torch.randn(5, vocab, device=DEV)
+    lg[0, 700] = lg[0, 33] = 50.0  # tie: the lower index wins
+    lg[1, vocab - 1] = 60.0
+    lg[2, 0] = 60.0
+    lg[3] = -3.0  # all equal
+    out = torch.empty(5, dtype=torch.int32, device=DEV)
+    slots = torch.tensor([4, -1, 0, 2, 1], dtype=torch.int32, device=DEV)
+    last = torch.full((6,), -7, dtype=torch.int32, device=DEV)
+    k.argmax_rows(lg, out, slots, last)
+    want = [33, vocab - 1, 0, 0, int(lg[4].argmax())]
+    assert out.tolist() == want
+    assert last.tolist() == [0, want[4], 0, -7, 33, -7]
+
+
+@pytest.mark.parametrize("vocab", [331, 1024, 151936])
+@pytest.mark.parametrize("temperature,top_k", [(0.7, 20), (1.0, 0), (1.3, 1), (0.5, 5000)])
+def test_sample_rows_matches_plain(vocab, temperature, top_k):
+    k = K()
+    rows = 6
+    g = torch.Generator().manual_seed(vocab + top_k)
+    lg = (torch.randn(rows, vocab, generator=g) * 3).float()
+    lg[1, 5] = lg[1, 100] = lg[1, 300] = lg[1].max() + 1.0  # ties at the top
+    lg[2, : min(50, vocab)] = 2.5                                # ties straddling the top-k boundary
+    seqs = torch.tensor([0, 1, 2, 3, 10, 999], dtype=torch.int32)
+    out = torch.empty(rows, dtype=torch.int32, device=DEV)
+    for step in (0, 1, 7):
+        k.sample_rows(lg.to(DEV), temperature, top_k, 1234, seqs.to(DEV), None, out, step_base=step)
+        got = out.tolist()
+        want = [P.choose_token(lg[r], temperature, top_k, P.uniform_draw(1234, int(seqs[r]), step)) for r in range(rows)]
+        assert got == want, (step, got, want)

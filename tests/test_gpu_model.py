@@ -1,0 +1,444 @@
+"""The engine against the plain implementation, in 32-bit and in bfloat16: each request alone and
+whole; with the last 32 tokens one by one; in batches of unequal lengths whose shorter requests end
+earlier, batch after batch so that slots are used again; long decoding; the first tokens of a
+sequence; generation through the entry point; parts alone; and a toy mixer with state of its own that
+is registered, built and stepped without touching the library's files."""
+
+import math
+
+import pytest
+import torch
+
+import helpers as H
+import plain_qwen3 as P
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+NAMES = ["a", "b", "c"]
+
+_engines = {}
+_plains = {}
+
+
+def engine_for(model_dirs, name, dtype, **kw):
+    from dryft_b200.engine.api import Engine
+
+    key = (name, dtype, tuple(sorted(kw.items())))
+    if key not in _engines:
+        opts = dict(dtype=dtype, max_batch=4, max_seq_len=512, max_tokens=4 * 512)
+        opts.update(kw)
+        _engines[key] = Engine(model_dirs[name], **opts)
+    return _engines[key]
+
+
+def plain_for(model_dirs, name, dtype):
+    key = (name, dtype)
+    if key not in _plains:
+        _plains[key] = P.load_plain(model_dirs[name], dtype)
+    return _plains[key]
+
+
+def check(got: torch.Tensor, name, tokens, rows, model_dirs, dtype, what=""):
+    """got [len(rows), V] vs the plain logits of the whole sequence at ``rows``."""
+    p32 = plain_for(model_dirs, name, torch.float32).logits(tokens)[rows]
+    got = got.float().cpu()
+    assert torch.isfinite(got).all(), what
+    if dtype == torch.float32:
+        e = H.rel_err(got, p32)
+        assert e <= H.FP32_TOL, f"{what}: 32-bit logits off by {e:.3g}"
+    else:
+        pb = plain_for(model_dirs, name, torch.bfloat16).logits(tokens)[rows]
+        tol = H.bf16_tol(pb, p32)
+        e = H.rel_err(got, pb)
+        assert e <= tol, f"{what}: bfloat16 logits off by {e:.3g} (allowed {tol:.3g})"
+
+
+def step(eng, slots, tokens, want):
+    with torch.inference_mode():
+        return eng.stepper.step(slots, tokens, want)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_whole_requests_alone(model_dirs, name, dtype):
+    eng = engine_for(model_dirs, name, dtype)
+    for i, n in enumerate([1, 2, 7, 31, 64, 65, 150]):
+        toks = H.prompts_for(name, [n], seed=i)[0]
+        (slot,) = eng.cache.open_sequences(1)
+        got = step(eng, [slot], [toks], [list(range(n))])
+        eng.cache.close_sequences([slot])
+        check(got, name, toks, list(range(n)), model_dirs, dtype, f"{name} whole len {n}")
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_last_32_tokens_one_by_one(model_dirs, name, dtype):
+    eng = engine_for(model_dirs, name, dtype)
+    for i, n in enumerate([33, 40, 100, 160]):
+        toks = H.prompts_for(name, [n], seed=10 + i)[0]
+        head = n - 32
+        (slot,) = eng.cache.open_sequences(1)
+        rows = [step(eng, [slot], [toks[:head]], [[head - 1]])]
+        for t in range(head, n):
+            rows.append(step(eng, [slot], [[toks[t]]], [[0]]))
+        eng.cache.close_sequences([slot])
+        got = torch.cat(rows)
+        check(got, name, toks, list(range(head - 1, n)), model_dirs, dtype, f"{name} len {n} last 32 one by one")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_unequal_batches_one_after_another(model_dirs, name, dtype):
+    """Requests of unequal total lengths start together with unequal prompts, go on one token each,
+    the shorter ones end earlier; three batches in a row on 4 slots so every slot is used again (the
+    second batch's sequences are longer than the first's, so stale keys would be seen if lengths
+    leaked)."""
+    eng = engine_for(model_dirs, name, dtype)
+    batches = [
+        [(5, 9), (13, 13), (1, 4)],             # (prompt length, total length)
+        [(31, 70), (7, 75), (16, 20), (64, 66)],
+        [(3, 40), (65, 67)],
+    ]
+    seed = 100
+    for bi, batch in enumerate(batches):
+        seqs = []
+        for (pl, tl) in batch:
+            seed += 1
+            seqs.append(H.prompts_for(name, [tl], seed=seed)[0])
+        slots = eng.cache.open_sequences(len(batch))
+        got = {i: [] for i in range(len(batch))}
+        rows_of = {i: [] for i in range(len(batch))}
+        out = step(eng, slots, [s[:pl] for s, (pl, _) in zip(seqs, batch)], [[pl - 1] for (pl, _) in batch])
+        for i, (pl, _) in enumerate(batch):
+            got[i].append(out[i:i + 1])
+            rows_of[i].append(pl - 1)
+        fed = [pl for (pl, _) in batch]
+        alive = [i for i, (pl, tl) in enumerate(batch) if pl < tl]
+        ended = [i for i in range(len(batch)) if i not in alive]
+        eng.cache.close_sequences([slots[i] for i in ended])  # ends right after its prompt
+        while alive:
+            out = step(eng, [slots[i] for i in alive], [[seqs[i][fed[i]]] for i in alive], [[0] for _ in alive])
+            for j, i in enumerate(alive):
+                got[i].append(out[j:j + 1])
+                rows_of[i].append(fed[i])
+                fed[i] += 1
+            done = [i for i in alive if fed[i] >= batch[i][1]]
+            eng.cache.close_sequences([slots[i] for i in done])
+            alive = [i for i in alive if i not in done]
+        for i in range(len(batch)):
+            check(torch.cat(got[i]), name, seqs[i], rows_of[i], model_dirs, dtype, f"{name} batch {bi} request {i}")
+        eng.cache.check()
+    assert eng.cache.slots.n_held == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["a", "c"])
+def test_long_decoding(model_dirs, name, dtype):
+    """A short prompt and 300 decoded tokens: crosses several pages and, for the windowed
+    configuration, leaves the window far behind."""
+    eng = engine_for(model_dirs, name, dtype)
+    n = 305
+    toks = H.prompts_for(name, [n], seed=77)[0]
+    (slot,) = eng.cache.open_sequences(1)
+    rows = [step(eng, [slot], [toks[:5]], [[4]])]
+    for t in range(5, n):
+        rows.append(step(eng, [slot], [[toks[t]]], [[0]]))
+    eng.cache.close_sequences([slot])
+    check(torch.cat(rows), name, toks, list(range(4, n)), model_dirs, dtype, f"{name} long decoding")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_first_tokens_of_a_sequence(model_dirs, name, dtype):
+    """A one-token prompt, then tokens one by one: positions 0, 1, 2, ... with nothing before them."""
+    eng = engine_for(model_dirs, name, dtype)
+    toks = H.prompts_for(name, [6], seed=5)[0]
+    (slot,) = eng.cache.open_sequences(1)
+    rows = [step(eng, [slot], [[t]], [[0]]) for t in toks]
+    eng.cache.close_sequences([slot])
+    check(torch.cat(rows), name, toks, list(range(6)), model_dirs, dtype, f"{name} first tokens")
+
+
+@pytest.mark.parametrize("name", NAMES)
+def test_cutting_invariance_32bit(model_dirs, name):
+    """In 32-bit the same request gives the same logits (to rounding) whole, in two chunks, and
+    inside a batch with other requests."""
+    eng = engine_for(model_dirs, name, torch.float32)
+    toks = H.prompts_for(name, [90], seed=31)[0]
+    other = H.prompts_for(name, [17, 130], seed=32)
+    s = eng.cache.open_sequences(1)
+    whole = step(eng, s, [toks], [list(range(90))]).cpu()
+    eng.cache.close_sequences(s)
+    s = eng.cache.open_sequences(1)
+    a = step(eng, s, [toks[:37]], [list(range(37))]).cpu()
+    b = step(eng, s, [toks[37:]], [list(range(53))]).cpu()
+    eng.cache.close_sequences(s)
+    assert H.rel_err(torch.cat([a, b]), whole) <= H.FP32_TOL
+    s = eng.cache.open_sequences(3)
+    out = step(eng, s, [other[0], toks, other[1]], [[], list(range(90)), [0]]).cpu()
+    eng.cache.close_sequences(s)
+    assert H.rel_err(out[:90], whole) <= H.FP32_TOL
+
+
+# ----------------------------------------------------------------------------- the entry point
+def _margins(plain, prompt, ours):
+    """Teacher-forced margin of each of our tokens under the plain model: max logit - logit[ours]
+    (the reference's replay margin, agent/verify.py:100-109)."""
+    lg = plain.logits(list(prompt) + list(ours[:-1]))[len(prompt) - 1:]
+    best = lg.max(dim=-1).values
+    mine = lg.gather(1, torch.tensor(ours)[:, None])[:, 0]
+    return (best - mine), lg
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,lengths,steps", [("a", [5, 9, 13], 8), ("b", [1, 7, 16, 31], 12), ("c", [30, 3], 50)])
+def test_greedy_generation_through_entry_point(model_dirs, name, lengths, steps, dtype):
+    eng = engine_for(model_dirs, name, dtype)
+    prompts = H.prompts_for(name, lengths, seed=3)
+    out = [s for s in eng.generate(prompts, steps)]
+    assert len(out) == steps and all(len(s) == len(prompts) for s in out)
+    again = [s for s in eng.generate(prompts, steps)]
+    assert again == out, "second run differs from the first (stale state)"
+    plain = plain_for(model_dirs, name, torch.float32)
+    for b, p in enumerate(prompts):
+        ours = [s[b] for s in out]
+        if dtype == torch.float32:
+            want = P.plain_generate(plain, [p], steps)[0]
+            assert ours == want, f"{name} sequence {b}"
+        else:
+            m, lg = _margins(plain, p, ours)
+            assert float(m.max()) <= 0.05 * float(lg.abs().max()), f"{name} sequence {b}: margin {float(m.max()):.3g}"
+    eng.cache.check()
+    assert eng.cache.slots.n_held == 0
+
+
+def test_sampled_generation_matches_plain(model_dirs):
+    """Config B's workload: 4 prompts of 1/7/16/31 tokens, 12 steps at temperature 0.7, top-k 20."""
+    eng = engine_for(model_dirs, "b", torch.float32)
+    prompts = H.prompts_for("b", [1, 7, 16, 31], seed=9)
+    out = [s for s in eng.generate(prompts, 12, temperature=0.7, top_k=20, seed=42)]
+    plain = plain_for(model_dirs, "b", torch.float32)
+    want = P.plain_generate(plain, prompts, 12, temperature=0.7, top_k=20, seed=42)
+    for b in range(4):
+        assert [s[b] for s in out] == want[b]
+    # the draws of a sequence do not depend on the batch it is in
+    alone = [s[0] for s in eng.generate([prompts[2]], 12, temperature=0.7, top_k=20, seed=42)]
+    assert alone == P.plain_generate(plain, [prompts[2]], 12, temperature=0.7, top_k=20, seed=42)[0]
+
+
+def test_stop_tokens_and_batches_in_a_row(model_dirs):
+    """More requests than slots, stop tokens that end some sequences early: -1 afterwards, slots
+    reused by the next batch, results equal to the plain model's."""
+    eng = engine_for(model_dirs, "a", torch.float32)
+    plain = plain_for(model_dirs, "a", torch.float32)
+    prompts = H.prompts_for("a", [4, 11, 2, 19, 6, 33, 9, 5, 12, 3], seed=21)
+    free_run = P.plain_generate(plain, prompts, 10)
+    stops = sorted({free_run[1][3], free_run[4][0], free_run[7][6]})
+    want = P.plain_generate(plain, prompts, 10, stop_token_ids=stops)
+    got = eng.generate_many(prompts, 10, stop_token_ids=stops)
+    assert got == want
+    steps = [s for s in eng.generate(prompts[:4], 10, stop_token_ids=stops)]
+    for b in range(4):
+        col = [s[b] for s in steps]
+        n = len(want[b])
+        assert col[:n] == want[b] and all(t == -1 for t in col[n:])
+    eng.cache.check()
+    assert eng.cache.slots.n_held == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_cuda_graph_decode_equals_eager(model_dirs, dtype):
+    g = engine_for(model_dirs, "b", dtype)
+    e = engine_for(model_dirs, "b", dtype, cuda_graphs=False)
+    prompts = H.prompts_for("b", [9, 2, 40], seed=8)
+    a = [s for s in g.generate(prompts, 20)]
+    b = [s for s in e.generate(prompts, 20)]
+    assert a == b
+    # sequences leaving mid-way change the padded batch: still equal
+    stop = [a[5][1]]
+    assert [s for s in g.generate(prompts, 20, stop_token_ids=stop)] == [s for s in e.generate(prompts, 20, stop_token_ids=stop)]
+
+
+def test_requests_beyond_capacity_are_refused(model_dirs):
+    eng = engine_for(model_dirs, "a", torch.float32)
+    with pytest.raises(ValueError):
+        list(eng.generate(H.prompts_for("a", [3] * 5), 4))           # more sequences than max_batch
+    with pytest.raises(ValueError):
+        list(eng.generate(H.prompts_for("a", [500]), 100))           # longer than max_seq_len
+    with pytest.raises(ValueError):
+        list(eng.generate([[1, 2], []], 4))                          # empty prompt
+    with pytest.raises(ValueError):
+        list(eng.generate([[1, 999999]], 4))                         # token outside the vocabulary
+    assert list(eng.generate([], 4)) == [] and list(eng.generate([[1]], 0)) == []
+    eng.cache.check()
+    assert eng.cache.slots.n_held == 0
+
+
+# ----------------------------------------------------------------------------- parts alone
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_parts_alone(dtype):
+    """Norm, feed-forward and attention mixer built from specs at sizes of their own (not a model's),
+    against the plain functions."""
+    from dryft_b200.cache.store import SequenceCache
+    from dryft_b200.config.spec import PartSpec
+    from dryft_b200.ops import kernels as K
+    from dryft_b200.parts import FFNS, MIXERS, NORMS, Runtime, StepContext
+    from dryft_b200.parts.base import TensorInfo
+    from dryft_b200.weights import RandomSource
+
+    dev = torch.device("cuda:0")
+    rt = Runtime(dtype=dtype, device=dev, sm_count=torch.cuda.get_device_properties(dev).multi_processor_count)
+    hidden, inter, nh, nkv, d = 72, 200, 6, 3, 32
+    attn_params = {"hidden_size": hidden, "num_heads": nh, "num_kv_heads": nkv, "head_dim": d, "scale": 0.2,
+                   "window": None, "qk_norm": PartSpec("rmsnorm", {"size": d, "eps": 1e-5}),
+                   "position": PartSpec("rope", {"rotary_dim": d, "theta": 12345.0})}
+    ffn_params = {"hidden_size": hidden, "intermediate_size": inter}
+    norm_params = {"size": hidden, "eps": 2e-6}
+    exp = {}
+    exp.update(NORMS.get("rmsnorm").tensors(norm_params, "n."))
+    exp.update(FFNS.get("swiglu").tensors(ffn_params, "f."))
+    exp.update(MIXERS.get("attention").tensors(attn_params, "m."))
+    src = RandomSource(exp, 5, dtype, dev, std=0.1)
+    cpu = {n: src._read(n).cpu() for n in exp}
+    cpu = {n: (t.float() if dtype == torch.float32 else t) for n, t in cpu.items()}
+    tol = 3e-2 if dtype == torch.bfloat16 else 1e-4
+    with torch.inference_mode():
+        norm = NORMS.get("rmsnorm")(norm_params, "n.", src, rt)
+        ffn = FFNS.get("swiglu")(ffn_params, "f.", src, rt)
+        mixer = MIXERS.get("attention")(attn_params, "m.", src, rt)
+        x = torch.randn(21, hidden, device=dev).to(dtype)
+        torch.testing.assert_close(norm.forward(x).cpu().float(), P.rmsnorm(x.cpu(), cpu["n.weight"], 2e-6).float(), rtol=tol, atol=tol)
+        got = ffn.forward(x, None).cpu().float()
+        ref = P.swiglu(x.cpu(), cpu["f.gate_proj.weight"], cpu["f.up_proj.weight"], cpu["f.down_proj.weight"], dtype).float()
+        torch.testing.assert_close(got, ref, rtol=tol, atol=tol)
+        # the mixer over two sequences (13 and 8 tokens) in one step, through a cache of its own
+        cache = SequenceCache([(mixer.kv_need(), None)], [None], max_tokens=256, max_slots=2, max_seq_len=128,
+                              page_size=64, dtype=dtype, device=dev)
+        slots = cache.open_sequences(2)
+        lens = [13, 8]
+        for s, n in zip(slots, lens):
+            cache.reserve(s, n)
+        cache.flush()
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+        cu, tok_slot, tok_pos = i32([0, 13, 21]), torch.empty(21, dtype=torch.int32, device=dev), torch.empty(21, dtype=torch.int32, device=dev)
+        K.step_meta(cu, i32(slots), cache.seq_len, tok_slot, tok_pos, 21, 2)
+        ctx = StepContext(n_tokens=21, n_seqs=2, tokens=i32([0] * 21), cu_q=cu, seq_slot=i32(slots), tok_slot=tok_slot,
+                          tok_pos=tok_pos, decode=False, tile_tok0=i32([0, 13]), tile_rows=i32([13, 8]), n_tiles=2, tile_size=64)
+        got = mixer.forward(x, ctx, cache.entry(0), None, True).cpu().float()
+        refs = []
+        for lo, n in ((0, 13), (13, 8)):
+            h = x[lo:lo + n].cpu()
+            q = P.matmul_nt(h, cpu["m.q_proj.weight"], dtype).view(n, nh, d)
+            k = P.matmul_nt(h, cpu["m.k_proj.weight"], dtype).view(n, nkv, d)
+            v = P.matmul_nt(h, cpu["m.v_proj.weight"], dtype).view(n, nkv, d)
+            q = P.rmsnorm(q, cpu["m.q_norm.weight"], 1e-5)
+            k = P.rmsnorm(k, cpu["m.k_norm.weight"], 1e-5)
+            cos, sin = P.rope_cos_sin(torch.arange(n), d, 12345.0, dtype)
+            o = P.causal_attention(P.apply_rope(q, cos, sin), P.apply_rope(k, cos, sin), v, 0.2, None, dtype)
+            refs.append(P.matmul_nt(o, cpu["m.o_proj.weight"], dtype).float())
+        torch.testing.assert_close(got, torch.cat(refs), rtol=tol, atol=tol)
+
+
+# ----------------------------------------------------------------------------- a toy mixer with state
+def test_toy_mixer_with_state_registers_builds_and_steps():
+    """A mixer that keeps a running sum of its inputs per sequence (fixed-size state, no keys or
+    values), defined here, registered under a new kind, put into a new architecture whose layers
+    alternate it with attention, built with random weights and stepped — whole prompts, token by
+    token, and on a reused slot — without a change to any file of the library."""
+    from dryft_b200.cache.store import StateNeed
+    from dryft_b200.config import register_architecture, unregister_architecture
+    from dryft_b200.config.spec import LayerSpec, ModelSpec, PartSpec, RunStep
+    from dryft_b200.engine.api import Engine
+    from dryft_b200.parts import MIXERS, TensorInfo, register_mixer
+    from dryft_b200.parts.linear import linear
+
+    class RunningMean:
+        @staticmethod
+        def tensors(params, prefix):
+            return {prefix + "mix.weight": TensorInfo((params["hidden_size"], params["hidden_size"]), "matrix")}
+
+        def __init__(self, params, prefix, weights, rt):
+            self.rt = rt
+            self.hidden = params["hidden_size"]
+            self.w = weights.load(prefix + "mix.weight", "matrix")
+
+        def kv_need(self):
+            return None
+
+        def state_need(self):
+            return StateNeed((self.hidden,), torch.float32)
+
+        def forward(self, h, ctx, cache, state, owns_cache=True):
+            # mean of the sequence's inputs up to and including each token; the running sum is the state
+            out = torch.zeros_like(h, dtype=torch.float32)
+            cu = ctx.cu_q.tolist()
+            slots = ctx.seq_slot.tolist()
+            for b, slot in enumerate(slots):
+                if slot < 0:
+                    continue
+                rows = h[cu[b]:cu[b + 1]].float()
+                sums = state[slot][None, :] + torch.cumsum(rows, dim=0)
+                pos = ctx.tok_pos[cu[b]:cu[b + 1]].float()[:, None]
+                out[cu[b]:cu[b + 1]] = sums / (pos + 1.0)
+                state[slot] = sums[-1]
+            return linear(out.to(h.dtype), self.w, self.rt)
+
+    class ToyConfig:
+        def __init__(self, raw):
+            self.raw = dict(raw)
+
+        def to_dict(self):
+            return dict(self.raw)
+
+        def model_spec(self):
+            r = self.raw
+            H_, V = r["hidden_size"], r["vocab_size"]
+            norm = PartSpec("rmsnorm", {"size": H_, "eps": 1e-6})
+            attn = PartSpec("attention", {"hidden_size": H_, "num_heads": 2, "num_kv_heads": 1, "head_dim": 16,
+                                          "scale": 0.25, "window": None, "qk_norm": None,
+                                          "position": PartSpec("rope", {"rotary_dim": 8, "theta": 100.0})})
+            toy = PartSpec("toy_running_mean", {"hidden_size": H_})
+            ffn = PartSpec("swiglu", {"hidden_size": H_, "intermediate_size": 48})
+            layers = tuple(LayerSpec("prenorm", m, ffn, norm, norm, f"l{i}.mixer.", f"l{i}.ffn.", f"l{i}.n1.", f"l{i}.n2.")
+                           for i, m in enumerate([toy, attn, toy]))
+            # run order names layer 0 twice (shared weights, separate state)
+            sched = (RunStep(0), RunStep(1), RunStep(2), RunStep(0))
+            return ModelSpec("ToyForCausalLM", V, H_, 256, PartSpec("embedding", {"vocab_size": V, "hidden_size": H_}),
+                             layers, sched, norm, PartSpec("lm_head", {"vocab_size": V, "hidden_size": H_, "tied": True}),
+                             embedding_prefix="emb.", final_norm_prefix="fn.", head_prefix="head.")
+
+    register_mixer("toy_running_mean", RunningMean)
+    register_architecture("ToyForCausalLM", ToyConfig)
+    try:
+        raw = {"architectures": ["ToyForCausalLM"], "hidden_size": 32, "vocab_size": 97}
+        eng = Engine.from_config(raw, seed=3, std=0.2, dtype="float32", max_batch=2, max_seq_len=128, max_tokens=256)
+        toks = torch.randint(0, 97, (20,), generator=torch.Generator().manual_seed(0)).tolist()
+        with torch.inference_mode():
+            s = eng.cache.open_sequences(1)
+            whole = eng.stepper.step(s, [toks], [list(range(20))]).cpu()
+            eng.cache.close_sequences(s)
+            # same slot again (reuse): the state must start from zero; feed in pieces
+            s2 = eng.cache.open_sequences(1)
+            assert s2 == s
+            parts = [eng.stepper.step(s2, [toks[:7]], [list(range(7))]).cpu()]
+            for t in toks[7:]:
+                parts.append(eng.stepper.step(s2, [[t]], [[0]]).cpu())
+            eng.cache.close_sequences(s2)
+            # and as one of two sequences in a batch
+            s3 = eng.cache.open_sequences(2)
+            both = eng.stepper.step(s3, [toks[:5], toks], [[], list(range(20))]).cpu()
+            eng.cache.close_sequences(s3)
+        assert torch.isfinite(whole).all() and float(whole.abs().max()) > 0
+        assert H.rel_err(torch.cat(parts), whole) <= H.FP32_TOL
+        assert H.rel_err(both, whole) <= H.FP32_TOL
+        # the state matters: the logits at the last place depend on the first token
+        with torch.inference_mode():
+            s = eng.cache.open_sequences(1)
+            other = eng.stepper.step(s, [[(toks[0] + 1) % 97] + toks[1:]], [[19]]).cpu()
+            eng.cache.close_sequences(s)
+        assert H.rel_err(other, whole[19:20]) > 1e-3
+    finally:
+        MIXERS.unregister("toy_running_mean")
+        unregister_architecture("ToyForCausalLM")
