@@ -151,6 +151,8 @@ class _DeviceBackend:
         self.e = engine
         self.h2d_bytes = 0
         self.d2h_bytes = 0
+        self._seq_key = None
+        self._seq_dev = None
 
     def open(self, n: int) -> List[int]:
         return self.e.cache.open_sequences(n)
@@ -175,10 +177,15 @@ class _DeviceBackend:
         n = len(handles)
         logits = e.stepper.decode_from_state(handles)
         bucket = logits.shape[0]
-        slots = list(handles) + [-1] * (bucket - n)
-        seqs = list(seq_ids) + [0] * (bucket - n)
-        chosen = choose(logits, params, row_seq=self._ints(seqs) if not params.greedy else None, step=step,
-                        row_slot=self._ints(slots), last_token=e.cache.last_token)
-        self.h2d_bytes += 4 * bucket * (2 if params.greedy else 3)
+        row_seq = None
+        if not params.greedy:
+            key = tuple(seq_ids) + (bucket,)
+            if self._seq_key != key:  # changes only when a sequence leaves the batch
+                self._seq_key, self._seq_dev = key, self._ints(list(seq_ids) + [0] * (bucket - n))
+                self.h2d_bytes += 4 * bucket
+            row_seq = self._seq_dev
+        chosen = choose(logits, params, row_seq=row_seq, step=step, row_slot=e.stepper.last_decode_slots,
+                        last_token=e.cache.last_token)
+        self.h2d_bytes += 4 * bucket  # the step's slot list, staged in pinned memory
         self.d2h_bytes += 4 * n
         return chosen[:n].tolist()

@@ -36,6 +36,7 @@ class Stepper:
         self._graphs: Dict[int, "_DecodeGraph"] = {}
         self._pinned: Optional[torch.Tensor] = None
         self._upload_event: Optional[torch.cuda.Event] = None
+        self.last_decode_slots: Optional[torch.Tensor] = None
 
     # ------------------------------------------------------------------ host -> device metadata
     def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], want: Sequence[Sequence[int]]) -> Optional[torch.Tensor]:
@@ -143,6 +144,7 @@ class Stepper:
         logits = g.run(slots)
         for s in slots:
             self.cache.advanced(s, 1)
+        self.last_decode_slots = g.seq_slot  # int32 [bucket] on the device, -1 for padding rows
         return logits
 
 
@@ -163,7 +165,10 @@ class _DecodeGraph:
         self.st = stepper
         self.bucket = bucket
         dev = stepper.rt.device
-        self.slot_host = torch.full((bucket,), -1, dtype=torch.int32).pin_memory()
+        # pinned staging for the per-step slot list: a ring, so the host may run several steps ahead
+        self.ring = [torch.full((bucket,), -1, dtype=torch.int32).pin_memory() for _ in range(8)]
+        self.ring_events: list = [None] * 8
+        self.ring_at = 0
         self.seq_slot = torch.full((bucket,), -1, dtype=torch.int32, device=dev)
         self.cu_q = torch.arange(bucket + 1, dtype=torch.int32, device=dev)
         self.tokens = torch.zeros(bucket, dtype=torch.int32, device=dev)
@@ -173,7 +178,7 @@ class _DecodeGraph:
         self.logits: Optional[torch.Tensor] = None
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.h2d_bytes = 4 * bucket
-        self._copied: Optional[torch.cuda.Event] = None
+        self.n_kernels = 0      # launches of this library's kernels in one step
 
     def _body(self) -> torch.Tensor:
         st = self.st
@@ -187,13 +192,17 @@ class _DecodeGraph:
 
     def run(self, slots: Sequence[int]) -> torch.Tensor:
         n = len(slots)
-        if self._copied is not None:
-            self._copied.synchronize()  # the last copy out of the pinned buffer has finished
-        self.slot_host[:n] = torch.tensor(list(slots), dtype=torch.int32)
-        self.slot_host[n:] = -1
-        self.seq_slot.copy_(self.slot_host, non_blocking=True)
-        self._copied = torch.cuda.Event()
-        self._copied.record()
+        i = self.ring_at
+        self.ring_at = (i + 1) % len(self.ring)
+        if self.ring_events[i] is not None:
+            self.ring_events[i].synchronize()  # the copy that last used this staging buffer has finished
+        host = self.ring[i]
+        host[:n] = torch.tensor(list(slots), dtype=torch.int32)
+        host[n:] = -1
+        self.seq_slot.copy_(host, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.ring_events[i] = ev
         if not self.st.cuda_graphs:
             return self._body()
         if self.graph is None:
@@ -208,8 +217,11 @@ class _DecodeGraph:
             torch.cuda.current_stream().wait_stream(side)
             torch.cuda.synchronize()
             self.graph = torch.cuda.CUDAGraph()
+            before = K.launch_count
             with torch.cuda.graph(self.graph):
                 self.logits = self._body()
-            self.seq_slot.copy_(self.slot_host, non_blocking=True)
+            self.n_kernels = K.launch_count - before
+            self.seq_slot.copy_(host, non_blocking=True)
         self.graph.replay()
+        K.launch_count += self.n_kernels
         return self.logits

@@ -143,8 +143,13 @@ def _act(t: torch.Tensor, name: str) -> int:
     raise KernelError(f"{name}: activations are float32 or bfloat16, got {t.dtype}")
 
 
-def _ok(rc: int, what: str) -> None:
+launch_count = 0  # kernels of this library launched (or captured into a graph) so far
+
+
+def _ok(rc: int, what: str, n_kernels: int = 1) -> None:
+    global launch_count
     if rc == 0:
+        launch_count += n_kernels
         return
     if rc == UNSUPPORTED:
         raise KernelError(f"{what}: sizes not supported by this kernel")
@@ -281,7 +286,8 @@ def attn_rows(q, k_pages, v_pages, page_table, tok_slot, tok_pos, out, scale: fl
     lib = attention_rows_lib(head_dim, n_heads // n_kv, page)
     _ok(lib.dryft_attn_rows(is_bf16, _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(page_table), page_table.shape[1],
                             _ptr(tok_slot), _ptr(tok_pos), _ptr(out), _ptr(part_o), _ptr(part_ml), n, n_kv, n_splits,
-                            float(scale), int(window or 0), _stream()), f"attn_rows (head_dim {head_dim})")
+                            float(scale), int(window or 0), _stream()), f"attn_rows (head_dim {head_dim})",
+        n_kernels=2 if n_splits > 1 else 1)
 
 
 def attn_prefill(q, k_pages, v_pages, page_table, tile_tok0, tile_rows, tok_slot, tok_pos, out, n_tiles: int,
