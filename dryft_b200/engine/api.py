@@ -46,6 +46,8 @@ class EngineOptions:
     cuda_graphs: bool = True
     device: str = "cuda:0"
     small_m_max: int = 16
+    fuse_decode: bool = True               # fold norms, adds and SiLU*mul into the decode products
+    pdl: bool = True                       # programmatic dependent launch between the decode products
 
 
 def _require_cuda(device: str) -> torch.device:
@@ -94,7 +96,7 @@ class Engine:
         self.dtype = dtype
         props = torch.cuda.get_device_properties(dev)
         self.rt = Runtime(dtype=dtype, device=dev, page_size=opts.page_size, sm_count=props.multi_processor_count,
-                          small_m_max=opts.small_m_max)
+                          small_m_max=opts.small_m_max, fuse_decode=opts.fuse_decode, pdl=opts.pdl)
         with torch.cuda.device(dev), torch.no_grad():
             self.model = DecoderModel(spec, source, self.rt)
             self.max_seq_len = opts.max_seq_len or min(spec.max_positions, 8192)

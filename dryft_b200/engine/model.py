@@ -15,7 +15,7 @@ import torch
 
 from ..cache.store import KVNeed, SequenceCache, StateNeed
 from ..config.spec import ModelSpec
-from ..parts.base import BLOCKS, EMBEDDINGS, FFNS, HEADS, MIXERS, NORMS, Runtime, StepContext
+from ..parts.base import BLOCKS, EMBEDDINGS, FFNS, HEADS, MIXERS, NORMS, Residual, Runtime, StepContext
 
 
 class DecoderModel:
@@ -61,18 +61,22 @@ class DecoderModel:
                 visit(part)
         return total
 
-    def forward(self, ctx: StepContext, cache: SequenceCache, want_rows: Optional[torch.Tensor], n_want: int) -> Optional[torch.Tensor]:
+    def forward(self, ctx: StepContext, cache: SequenceCache, want_rows: Optional[torch.Tensor], n_want: int,
+                all_rows: bool = False) -> Optional[torch.Tensor]:
         """Run the step's tokens through every run step; logits ``[n_want, vocab]`` float32 at the
-        packed rows ``want_rows`` (None if nothing is wanted)."""
-        x = self.embedding.forward(ctx.tokens, ctx.n_tokens)
-        delta = None
+        packed rows ``want_rows`` (None if nothing is wanted).  ``all_rows`` says that ``want_rows`` is simply
+        every row in order (a decode step), which lets the head take the fused path."""
+        res = Residual(self.embedding.forward(ctx.tokens, ctx.n_tokens))
         for i, st in enumerate(self.spec.schedule):
             block = self.blocks[st.layer]
-            x, delta = block.forward(x, delta, ctx, cache.entry(i), cache.state(i), owns_cache=st.cache_from is None)
+            res = block.forward(res, ctx, cache.entry(i), cache.state(i), owns_cache=st.cache_from is None)
         if n_want == 0:
             return None
-        if delta is None:
-            h = self.final_norm.forward(x, rows=want_rows, n_rows=n_want)
+        if (all_rows and res.delta is None and res.ss is not None and hasattr(self.head, "forward_normed")
+                and self.head.can_fuse(res.x.shape[0], self.final_norm)):
+            return self.head.forward_normed(res.x, res.ss, res.ss_parts, self.final_norm)
+        if res.delta is None:
+            h = self.final_norm.forward(res.x, rows=want_rows, n_rows=n_want)
         else:
-            h = self.final_norm.add_forward(x, delta, rows=want_rows, n_rows=n_want)
+            h = self.final_norm.add_forward(res.x, res.delta, rows=want_rows, n_rows=n_want)
         return self.head.forward(h)

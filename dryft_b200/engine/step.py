@@ -186,7 +186,7 @@ class _DecodeGraph:
         K.step_meta(self.cu_q, self.seq_slot, st.cache.seq_len, self.tok_slot, self.tok_pos, self.bucket, self.bucket)
         ctx = StepContext(n_tokens=self.bucket, n_seqs=self.bucket, tokens=self.tokens, cu_q=self.cu_q,
                           seq_slot=self.seq_slot, tok_slot=self.tok_slot, tok_pos=self.tok_pos, decode=True)
-        logits = st.model.forward(ctx, st.cache, self.rows, self.bucket)
+        logits = st.model.forward(ctx, st.cache, self.rows, self.bucket, all_rows=True)
         K.step_advance(self.cu_q, self.seq_slot, st.cache.seq_len, self.bucket)
         return logits
 

@@ -61,10 +61,11 @@ def core() -> ctypes.CDLL:
             lib.dryft_gemm_nt_f32.argtypes = [_p, _i, _p, _p, _i, _i, _i, _i, _p]
             lib.dryft_argmax_rows.argtypes = [_p, _i, _i, _ll, _p, _p, _p, _p]
             lib.dryft_sample_rows.argtypes = [_p, _i, _i, _ll, _f, _i, _ull, _p, _p, _i, _p, _p, _p, _p]
-            lib.dryft_gemm_small_m.argtypes = [_p, _i, _p, _p, _i, _i, _i, _i, _i, _p]
+            lib.dryft_gemm_small_m.argtypes = [_p, _i, _p, _p, _i, _i, _i, _i, _i, _p, _p, _i, _f, _p, _i, _p]
+            lib.dryft_row_sumsq.argtypes = [_p, _i, _i, _p, _p]
             for name in ("dryft_step_meta", "dryft_step_advance", "dryft_tokens_from_state", "dryft_embed",
                          "dryft_rmsnorm", "dryft_residual_add", "dryft_silu_mul", "dryft_qk_norm_rope_store",
-                         "dryft_gemm_nt_f32", "dryft_argmax_rows", "dryft_sample_rows", "dryft_gemm_small_m"):
+                         "dryft_gemm_nt_f32", "dryft_argmax_rows", "dryft_sample_rows", "dryft_gemm_small_m", "dryft_row_sumsq"):
                 getattr(lib, name).restype = _i
             _core = lib
         return _core
@@ -144,6 +145,25 @@ def _act(t: torch.Tensor, name: str) -> int:
 
 
 launch_count = 0  # kernels of this library launched (or captured into a graph) so far
+
+_error_flags: Dict[int, torch.Tensor] = {}
+
+
+def error_flag(device: torch.device) -> torch.Tensor:
+    """The device int that kernels with bounded waits raise when a wait runs out."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _error_flags:
+        _error_flags[idx] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+    return _error_flags[idx]
+
+
+def check_error_flags() -> None:
+    """Raise if any kernel gave up a bounded wait since the last check (reads the flag: a sync)."""
+    for idx, flag in _error_flags.items():
+        if int(flag.item()) != 0:
+            flag.zero_()
+            raise KernelError(f"a kernel on cuda:{idx} gave up waiting for its own copies (bounded wait ran out); "
+                              "results since the last check are not valid")
 
 
 def _ok(rc: int, what: str, n_kernels: int = 1) -> None:
@@ -327,18 +347,70 @@ def gemm_nt_f32(a, w, out) -> None:
     _ok(core().dryft_gemm_nt_f32(_ptr(a), k, _ptr(w), _ptr(out), n, m, n, k, _stream()), "gemm_nt_f32")
 
 
-def gemm_small_m(a, w, out) -> None:
-    """``out[M,N] = a[M,K] @ w[N,K].T`` for a handful of rows (decode): bfloat16 operands, 32-bit
-    accumulation, ``out`` bfloat16 or float32.  Every weight byte is read once."""
+SMALL_M_LIMIT = 16  # rows the weight-streaming product takes
+SS_STRIDE = 64  # floats per block in the sum-of-squares buffers of the fused decode products
+
+
+def gemm_small_m(a, w, out, *, mode: str = "store", norm_w=None, ss_in=None, ss_parts: int = 0, eps: float = 0.0,
+                 ss_out=None, pdl: bool = False) -> None:
+    """``a[M,K] @ w[.,K].T`` for up to 16 rows (decode; K a multiple of 16): bfloat16 operands, 32-bit accumulation,
+    every weight byte read once.  ``mode``:
+
+    * ``"store"``: ``out[M,N]`` (bfloat16 or float32) receives the product, ``w`` is ``[N,K]``;
+    * ``"residual"``: ``out`` is the residual stream ``x[M,N]``, updated in place ``x += product``; with
+      ``ss_out`` ``[ceil(N/16), 64]`` float32 the per-row sums of squares of the new ``x`` are left there,
+      one partial per block of 16 columns;
+    * ``"silu"``: ``w`` is ``[2N,K]`` (gate rows, then up rows) and ``out[M,N] = silu(gate) * up``.
+
+    With ``norm_w`` ``[K]`` float32 the rows of ``a`` are RMS-normalised on the fly; ``ss_in``
+    ``[ss_parts, 64]`` holds their sums of squares as an earlier ``"residual"`` product (or ``row_sumsq``)
+    left them.  ``pdl`` launches the kernel as a programmatic dependent of the launch before it: its
+    first weight requests overlap that launch's tail."""
     m, k = a.shape
-    n = w.shape[0]
     _need(a, "a", torch.bfloat16)
-    _need(w, "w", torch.bfloat16, (n, k))
-    _need(out, "out", None, (m, n))
-    if out.dtype not in (torch.bfloat16, torch.float32):
-        raise KernelError(f"gemm_small_m: output must be bfloat16 or float32, got {out.dtype}")
-    _ok(core().dryft_gemm_small_m(_ptr(a), k, _ptr(w), _ptr(out), n, int(out.dtype == torch.float32), m, n, k, _stream()),
-        f"gemm_small_m (M={m}, N={n}, K={k})")
+    if mode == "silu":
+        n = w.shape[0] // 2
+        _need(w, "w", torch.bfloat16, (2 * n, k))
+        _need(out, "out", torch.bfloat16, (m, n))
+        code = 3
+    elif mode == "residual":
+        n = w.shape[0]
+        _need(w, "w", torch.bfloat16, (n, k))
+        _need(out, "residual stream", torch.bfloat16, (m, n))
+        code = 2
+        if ss_out is not None:
+            _need(ss_out, "ss_out", torch.float32)
+            if ss_out.numel() < (n + 15) // 16 * SS_STRIDE:
+                raise KernelError("gemm_small_m: ss_out too small")
+    elif mode == "store":
+        n = w.shape[0]
+        _need(w, "w", torch.bfloat16, (n, k))
+        _need(out, "out", None, (m, n))
+        if out.dtype not in (torch.bfloat16, torch.float32):
+            raise KernelError(f"gemm_small_m: output must be bfloat16 or float32, got {out.dtype}")
+        code = int(out.dtype == torch.float32)
+    else:
+        raise KernelError(f"gemm_small_m: unknown mode {mode!r}")
+    if mode != "residual" and ss_out is not None:
+        raise KernelError("gemm_small_m: ss_out belongs to mode='residual'")
+    if norm_w is not None:
+        _need(norm_w, "norm_w", torch.float32, (k,))
+        _need(ss_in, "ss_in", torch.float32)
+        if ss_parts <= 0 or ss_in.numel() < ss_parts * SS_STRIDE:
+            raise KernelError("gemm_small_m: ss_in does not hold ss_parts blocks")
+    _ok(core().dryft_gemm_small_m(_ptr(a), k, _ptr(w), _ptr(out), n, code, m, n, k, _ptr(norm_w), _ptr(ss_in),
+                                  int(ss_parts), float(eps), _ptr(ss_out), int(pdl), _stream()),
+        f"gemm_small_m (M={m}, N={n}, K={k}, mode={mode})")
+
+
+def row_sumsq(x, ss) -> None:
+    """``ss[m] = sum(x[m]^2)`` for up to 64 rows of bfloat16 ``x``: one block of sums of squares."""
+    rows, hidden = x.shape
+    _need(x, "x", torch.bfloat16)
+    _need(ss, "ss", torch.float32)
+    if ss.numel() < SS_STRIDE:
+        raise KernelError("row_sumsq: ss holds fewer than 64 floats")
+    _ok(core().dryft_row_sumsq(_ptr(x), rows, hidden, _ptr(ss), _stream()), "row_sumsq")
 
 
 # ----------------------------------------------------------------------------- token choice

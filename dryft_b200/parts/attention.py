@@ -90,13 +90,38 @@ class Attention:
         want = math.ceil(2 * self.rt.sm_count / max(1, n_rows * self.n_kv))
         return max(1, min(32, want))
 
+    def can_fuse(self, n_rows: int, norm) -> bool:
+        """Few rows, bfloat16 everywhere, widths the weight-streaming product takes."""
+        rt = self.rt
+        return (rt.fuse_decode and rt.is_bf16 and n_rows <= min(rt.small_m_max, K.SMALL_M_LIMIT)
+                and type(norm).__name__ == "RMSNorm" and self.w_qkv.dtype == torch.bfloat16
+                and self.w_o.dtype == torch.bfloat16 and self.hidden % 16 == 0 and self.q_dim % 16 == 0)
+
+    def forward_normed(self, x, ss, ss_parts, norm, ctx, cache, state, owns_cache: bool = True):
+        """``x += o_proj(attention(qkv_proj(norm(x))))`` in place: the norm inside the first product,
+        the add inside the last, which also leaves the new sums of squares of ``x``."""
+        n = x.shape[0]
+        w = self.w_qkv if owns_cache else self.w_qkv[: self.q_dim]
+        qkv = torch.empty((n, w.shape[0]), dtype=x.dtype, device=x.device)
+        K.gemm_small_m(x, w, qkv, norm_w=norm.weight, ss_in=ss, ss_parts=ss_parts, eps=norm.eps, pdl=self.rt.pdl)
+        o = self._attend(qkv, ctx, cache, owns_cache)
+        parts = (self.hidden + 15) // 16
+        ss_out = torch.empty(parts * K.SS_STRIDE, dtype=torch.float32, device=x.device)
+        K.gemm_small_m(o, self.w_o, x, mode="residual", ss_out=ss_out, pdl=self.rt.pdl)
+        return ss_out, parts
+
     def forward(self, h: torch.Tensor, ctx: StepContext, cache: CacheEntry, state, owns_cache: bool = True) -> torch.Tensor:
-        n = h.shape[0]
-        dev = h.device
         if owns_cache:
             qkv = linear(h, self.w_qkv, self.rt)
         else:  # a run step that reads another step's cache projects queries only
             qkv = linear(h, self.w_qkv[: self.q_dim], self.rt)
+        return linear(self._attend(qkv, ctx, cache, owns_cache), self.w_o, self.rt)
+
+    def _attend(self, qkv: torch.Tensor, ctx: StepContext, cache: CacheEntry, owns_cache: bool) -> torch.Tensor:
+        """q/k norm + RoPE + cache write, then attention over the cache: ``[tokens, q_dim]``."""
+        n = qkv.shape[0]
+        dev = qkv.device
+        h = qkv
         q = torch.empty((n, self.n_heads, self.head_dim), dtype=h.dtype, device=dev)
         K.qk_norm_rope_store(qkv, self.q_norm_w, self.k_norm_w, self.position.inv_freq, ctx.tok_slot, ctx.tok_pos, q,
                              cache.k, cache.v, cache.page_table, self.n_heads, self.n_kv, self.head_dim,
@@ -113,4 +138,4 @@ class Attention:
                 part_ml = torch.empty((n, self.n_heads, s, 2), dtype=torch.float32, device=dev)
             K.attn_rows(q, cache.k, cache.v, cache.page_table, ctx.tok_slot, ctx.tok_pos, o, self.scale, self.window,
                         s, part_o, part_ml)
-        return linear(o, self.w_o, self.rt)
+        return o

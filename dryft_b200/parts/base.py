@@ -12,9 +12,14 @@ position    ``__init__(params, head_dim, rt)``; gives ``rotary_dim`` and ``inv_f
 mixer       ``tensors``; ``__init__``; ``kv_need()`` / ``state_need()``;
             ``forward(h, ctx, cache, state, owns_cache)`` -> ``[tokens, hidden]`` (not yet added).
 ffn         ``tensors``; ``__init__``; ``forward(h, ctx)`` -> ``[tokens, hidden]``.
-block       ``__init__(layer_spec, norm_mixer, mixer, norm_ffn, ffn)``;
-            ``forward(x, delta, ctx, cache, state, owns_cache)`` -> ``(x, delta)``: the residual stream and the
-            not-yet-added output of the block's last part, so the next norm can fuse the add.
+block       ``__init__(norm_mixer, mixer, norm_ffn, ffn)``;
+            ``forward(res, ctx, cache, state, owns_cache)`` -> ``Residual``: the stream, plus either the
+            not-yet-added output of the block's last part (so the next norm can fuse the add) or the
+            stream's sums of squares (so the next fused product can normalise it).
+Optional, for few rows (decode): a mixer or feed-forward may offer
+            ``forward_normed(x, ss, ss_parts, norm, ...) -> (ss, ss_parts)``: it normalises ``x`` itself
+            inside its first product, adds its output into ``x`` in place inside its last product, and
+            returns the new sums of squares; ``can_fuse(n_rows, norm)`` says when.
 """
 
 from __future__ import annotations
@@ -46,6 +51,8 @@ class Runtime:
     sm_count: int = 148
     small_m_max: int = 16        # decode rows up to which the weight-streaming product is used
     ffn_chunk_rows: int = 16384  # rows of the feed-forward processed at once (bounds [rows, 2I])
+    fuse_decode: bool = True     # few rows: fold norms, residual adds and SiLU*mul into the products
+    pdl: bool = True             # launch the fused decode products as programmatic dependents
 
     @property
     def is_bf16(self) -> bool:
@@ -69,6 +76,19 @@ class StepContext:
     n_tiles: int = 0
     tile_size: int = 0
     extras: Dict[str, Any] = field(default_factory=dict)
+
+
+@dataclass
+class Residual:
+    """The residual stream between blocks.  ``delta`` is the previous part's output that has not
+    been added to ``x`` yet (the next norm fuses the add).  ``ss`` holds per-row sums of squares of
+    ``x`` in ``ss_parts`` blocks of 64 floats, as the fused decode products leave them for the next
+    norm; it is only meaningful while ``delta`` is None."""
+
+    x: torch.Tensor
+    delta: Optional[torch.Tensor] = None
+    ss: Optional[torch.Tensor] = None
+    ss_parts: int = 0
 
 
 class Registry:

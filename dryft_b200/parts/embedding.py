@@ -65,3 +65,15 @@ class LMHead:
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         """32-bit logits ``[rows, vocab]``."""
         return linear(h, self.weight, self.rt, out_dtype=torch.float32)
+
+    def can_fuse(self, n_rows: int, norm) -> bool:
+        rt = self.rt
+        return (rt.fuse_decode and rt.is_bf16 and n_rows <= min(rt.small_m_max, K.SMALL_M_LIMIT)
+                and type(norm).__name__ == "RMSNorm" and self.weight.dtype == torch.bfloat16
+                and self.weight.shape[1] % 16 == 0)
+
+    def forward_normed(self, x: torch.Tensor, ss, ss_parts: int, norm) -> torch.Tensor:
+        """Logits of every row of ``x`` with the final norm inside the product (decode)."""
+        out = torch.empty((x.shape[0], self.vocab), dtype=torch.float32, device=x.device)
+        K.gemm_small_m(x, self.weight, out, norm_w=norm.weight, ss_in=ss, ss_parts=ss_parts, eps=norm.eps, pdl=self.rt.pdl)
+        return out

@@ -34,6 +34,24 @@ class SwiGLU:
             [prefix + "gate_proj.weight", prefix + "up_proj.weight"], [self.inter, self.inter], self.hidden)
         self.w_down = weights.load(prefix + "down_proj.weight", "matrix")
 
+    def can_fuse(self, n_rows: int, norm) -> bool:
+        rt = self.rt
+        return (rt.fuse_decode and rt.is_bf16 and n_rows <= min(rt.small_m_max, K.SMALL_M_LIMIT)
+                and type(norm).__name__ == "RMSNorm" and self.w_gate_up.dtype == torch.bfloat16
+                and self.w_down.dtype == torch.bfloat16 and self.hidden % 16 == 0 and self.inter % 16 == 0)
+
+    def forward_normed(self, x, ss, ss_parts, norm, ctx):
+        """``x += down(silu(gate(norm(x))) * up(norm(x)))`` in place, two launches: the norm and the
+        SiLU*mul inside the first product, the add (and the new sums of squares) inside the second."""
+        n = x.shape[0]
+        act = torch.empty((n, self.inter), dtype=x.dtype, device=x.device)
+        K.gemm_small_m(x, self.w_gate_up, act, mode="silu", norm_w=norm.weight, ss_in=ss, ss_parts=ss_parts,
+                       eps=norm.eps, pdl=self.rt.pdl)
+        parts = (self.hidden + 15) // 16
+        ss_out = torch.empty(parts * K.SS_STRIDE, dtype=torch.float32, device=x.device)
+        K.gemm_small_m(act, self.w_down, x, mode="residual", ss_out=ss_out, pdl=self.rt.pdl)
+        return ss_out, parts
+
     def _rows(self, h: torch.Tensor) -> torch.Tensor:
         gu = linear(h, self.w_gate_up, self.rt)
         act = torch.empty((h.shape[0], self.inter), dtype=h.dtype, device=h.device)

@@ -40,7 +40,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, rt: Runtime, out_dtype: Optional[to
         return out if out_dtype == torch.float32 else out.to(out_dtype)
     if w.dtype != torch.bfloat16:
         raise ValueError(f"linear: weight dtype {w.dtype} is not supported")
-    if m <= rt.small_m_max and k % 8 == 0:
+    if m <= min(rt.small_m_max, K.SMALL_M_LIMIT) and k % 16 == 0:
         out = torch.empty((m, n), dtype=out_dtype, device=x.device)
         K.gemm_small_m(x, w, out)
         return out

@@ -133,8 +133,8 @@ def test_gemm_f32(m, n, k_):
     assert torch.equal(out1[0], out[m - 1])
 
 
-@pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 17, 32, 33, 64])
-@pytest.mark.parametrize("n,k_", [(2560, 2560), (331, 96), (19, 4096), (6144, 1000), (48, 8)])
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("n,k_", [(2560, 2560), (331, 96), (19, 4096), (6144, 1008), (48, 16), (160, 9728)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_gemm_small_m(m, n, k_, out_dtype):
     k = K()
@@ -151,12 +151,65 @@ def test_gemm_small_m(m, n, k_, out_dtype):
     assert torch.equal(out1[0], out[0])
 
 
+@pytest.mark.parametrize("m", [1, 8, 13])
+@pytest.mark.parametrize("n,k_", [(2560, 2560), (96, 176), (200, 1008)])
+def test_gemm_small_m_fused_norm_residual_silu(m, n, k_):
+    """The fused forms of the decode product against the plain parts: RMSNorm of the input from
+    sums of squares left by an earlier product, residual add with new sums of squares, SiLU*mul."""
+    k = K()
+    bf = torch.bfloat16
+    eps = 1e-5
+    x = (torch.randn(m, k_, device=DEV) * 2).to(bf)
+    nw = (1 + 0.1 * torch.randn(k_, device=DEV)).to(bf).float()
+    w = (torch.randn(n, k_, device=DEV) / math.sqrt(k_)).to(bf)
+    ss = torch.zeros(64, device=DEV)
+    k.row_sumsq(x, ss)
+    torch.testing.assert_close(ss[:m].cpu(), x.float().pow(2).sum(-1).cpu(), rtol=1e-5, atol=1e-5)
+    h_ref = P.rmsnorm(x.cpu(), nw.cpu(), eps)
+    # norm prologue + plain store
+    out = torch.empty(m, n, device=DEV, dtype=bf)
+    k.gemm_small_m(x, w, out, norm_w=nw, ss_in=ss, ss_parts=1, eps=eps)
+    ref = h_ref.double() @ w.cpu().double().T
+    torch.testing.assert_close(out.cpu().double(), ref, rtol=2e-2, atol=2e-2)
+    # residual epilogue with sums of squares for the next norm
+    res = torch.randn(m, n, device=DEV).to(bf)
+    res0 = res.clone()
+    parts = (n + 15) // 16
+    ss_out = torch.full((parts * 64,), -1.0, device=DEV)
+    k.gemm_small_m(x, w, res, mode="residual", ss_out=ss_out)
+    prod = P.matmul_nt(x.cpu(), w.cpu(), bf)
+    want = P.residual_add(res0.cpu(), prod)
+    torch.testing.assert_close(res.cpu().float(), want.float(), rtol=2e-2, atol=2e-2)
+    got_ss = ss_out.view(parts, 64)[:, :m].sum(0).cpu()
+    torch.testing.assert_close(got_ss, res.float().pow(2).sum(-1).cpu(), rtol=1e-4, atol=1e-4)
+    # the sums chain: a second product normalises the new stream from them
+    if n % 16 == 0:
+        w2 = (torch.randn(48, n, device=DEV) / math.sqrt(n)).to(bf)
+        nw2 = (1 + 0.1 * torch.randn(n, device=DEV)).to(bf).float()
+        out2 = torch.empty(m, 48, device=DEV, dtype=torch.float32)
+        k.gemm_small_m(res, w2, out2, norm_w=nw2, ss_in=ss_out, ss_parts=parts, eps=eps)
+        ref2 = P.rmsnorm(res.cpu(), nw2.cpu(), eps).double() @ w2.cpu().double().T
+        torch.testing.assert_close(out2.cpu().double(), ref2, rtol=2e-2, atol=2e-2)
+    # SiLU*mul epilogue over gate rows then up rows
+    inter = n // 2
+    act = torch.empty(m, inter, device=DEV, dtype=bf)
+    k.gemm_small_m(x, w[: 2 * inter], act, mode="silu")
+    gu = P.matmul_nt(x.cpu(), w[: 2 * inter].cpu(), bf)
+    want = P.silu_mul(gu[:, :inter], gu[:, inter:])
+    torch.testing.assert_close(act.cpu().float(), want.float(), rtol=3e-2, atol=3e-2)
+
+
 def test_gemm_small_m_refuses_odd_k():
     k = K()
     a = torch.zeros(2, 12, device=DEV, dtype=torch.bfloat16)
     w = torch.zeros(4, 12, device=DEV, dtype=torch.bfloat16)
     with pytest.raises(k.KernelError):
         k.gemm_small_m(a, w, torch.empty(2, 4, device=DEV, dtype=torch.bfloat16))
+    a = torch.zeros(17, 32, device=DEV, dtype=torch.bfloat16)  # more rows than the kernel takes
+    w = torch.zeros(4, 32, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(k.KernelError):
+        k.gemm_small_m(a, w, torch.empty(17, 4, device=DEV, dtype=torch.bfloat16))
+    k.check_error_flags()
 
 
 # ------------------------------------------------------------------------------------ rope + cache write

@@ -261,6 +261,30 @@ def test_cuda_graph_decode_equals_eager(model_dirs, dtype):
     assert [s for s in g.generate(prompts, 20, stop_token_ids=stop)] == [s for s in e.generate(prompts, 20, stop_token_ids=stop)]
 
 
+def test_fused_decode_products_equal_the_separate_kernels(model_dirs):
+    """With few rows the norms, residual adds and SiLU*mul are folded into the matrix products and
+    launched as programmatic dependents; the logits must stay those of the separate kernels (same
+    rounding points, sums in another order), and switching the launch overlap off changes no bit."""
+    fused = engine_for(model_dirs, "b", torch.bfloat16)
+    plain_launch = engine_for(model_dirs, "b", torch.bfloat16, pdl=False)
+    separate = engine_for(model_dirs, "b", torch.bfloat16, fuse_decode=False)
+    toks = H.prompts_for("b", [40], seed=12)[0]
+    outs = []
+    for eng in (fused, plain_launch, separate):
+        s = eng.cache.open_sequences(1)
+        rows = [step(eng, s, [toks[:30]], [[29]])]
+        for t in toks[30:]:
+            rows.append(step(eng, s, [[t]], [[0]]))
+        eng.cache.close_sequences(s)
+        outs.append(torch.cat(rows).float().cpu())
+    assert torch.equal(outs[0], outs[1])
+    p32 = plain_for(model_dirs, "b", torch.float32).logits(toks)[29:]
+    pb = plain_for(model_dirs, "b", torch.bfloat16).logits(toks)[29:]
+    assert H.rel_err(outs[0], outs[2]) <= H.bf16_tol(pb, p32)
+    from dryft_b200.ops import kernels as K
+    K.check_error_flags()
+
+
 def test_requests_beyond_capacity_are_refused(model_dirs):
     eng = engine_for(model_dirs, "a", torch.float32)
     with pytest.raises(ValueError):
