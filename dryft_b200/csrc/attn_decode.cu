@@ -1,0 +1,450 @@
+// Decode attention in one launch (bfloat16): per-head q/k RMSNorm + rotate-half RoPE of the new
+// token, write of its K and V into the paged cache, attention of its GROUP query heads over the
+// cache split across blocks, and the combination of the splits — what hari495/dryft does in three
+// kernels (kernels/rope_qknorm.py:50-99 decode mapping; kernels/attn_decode.py:36-99 split-KV;
+// kernels/attn_decode.py:102-118 reduce).  Compiled per model with -DDRYFT_HEAD_DIM, -DDRYFT_GROUP,
+// -DDRYFT_PAGE.
+//
+// Grid (rows, kv heads, splits); a row is one sequence's new token.  Every block rebuilds the row's
+// GROUP rotated queries (cheap, and it saves a launch and a round trip through memory); the one block
+// whose page range holds the token's own position also makes the new key and value and writes them
+// into the cache before anyone in the block reads that page.  The GROUP query heads of the token form
+// the (zero-padded) 16-row operand of mma.sync.m16n8k16, so Q K^T and P V run on the tensor cores as
+// in the prefill kernel (csrc/attn_prefill.cu), with the heads where that kernel has query tokens.
+// Inside a block each warp walks over 16-key slices of its own (no block-wide barrier in the loop):
+// it requests the slice's K and V rows with cp.async into its own ring of shared-memory buffers, the
+// next slice in flight while one is used, the first requests going out before the queries are rebuilt (the
+// new token's own row is patched into the staged slice from shared memory, so the early request need
+// not wait for the cache write); scores, running maximum and sums are 32-bit
+// (attn_decode.py:77-90), P is rounded to bfloat16 for the second product (attn_decode.py:12-14,89).
+// The warps' partial (m, l, acc) are combined through shared memory.  With several splits each block
+// leaves its partial in global memory and takes a ticket; the block that draws the last ticket of a
+// (row, kv head) combines all partials in split order, so the result does not depend on arrival
+// order, and puts the ticket counter back to zero.  No block waits for another: there is no spin.
+//
+// Formulas and rounding points are those of csrc/rope_kv.cu and csrc/attn_prefill.cu.
+#include "common.cuh"
+#include <math.h>
+
+#if !defined(DRYFT_HEAD_DIM) || !defined(DRYFT_GROUP) || !defined(DRYFT_PAGE)
+#error "compile with -DDRYFT_HEAD_DIM=.. -DDRYFT_GROUP=.. -DDRYFT_PAGE=.."
+#endif
+
+namespace {
+typedef __nv_bfloat16 bf16;
+constexpr int D = DRYFT_HEAD_DIM;
+constexpr int G = DRYFT_GROUP;
+constexpr int PAGE = DRYFT_PAGE;
+constexpr int NWARP = 8;
+constexpr int THREADS = NWARP * 32;
+constexpr int SLICE = 16;                   // keys a warp handles at a time
+constexpr int SPP = PAGE / SLICE;           // slices per page
+constexpr int KS = D + 8;                   // padded row (elements): conflict-free ldmatrix
+constexpr int KSTEPS = D / 16;
+constexpr int DT = D / 8;
+static_assert(D % 16 == 0 && D <= 256, "head size 16..256 in steps of 16");
+static_assert(G >= 1 && G <= 16, "1..16 query heads per kv head");
+static_assert(PAGE % SLICE == 0, "page size must be a multiple of 16");
+// shared memory: Q [16][KS] bf16 and the new token's K and V rows, then per warp STAGES stages of
+// (K slice, V slice) [16][KS] bf16 each.
+// The combine buffers (m, l: [NWARP][16]; acc: [NWARP][G][D] floats) overlay the stages at the end.
+constexpr int STAGES = 2;                   // slices staged per warp (one in flight while one is used)
+constexpr size_t Q_BYTES = (size_t)(16 + 2) * KS * 2;      // 16 query rows, then the new key and the new value
+constexpr size_t WARP_STAGE_BYTES = (size_t)STAGES * 2 * SLICE * KS * 2;
+constexpr size_t COMBINE_BYTES = (size_t)NWARP * 16 * 2 * 4 + (size_t)NWARP * G * D * 4;
+constexpr size_t PIPE_BYTES = NWARP * WARP_STAGE_BYTES;
+constexpr size_t SMEM_BYTES = Q_BYTES + (PIPE_BYTES > COMBINE_BYTES ? PIPE_BYTES : COMBINE_BYTES);
+
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(s), "l"(gmem));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N)); }
+__device__ __forceinline__ void ldsm_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void ldsm_x4_t(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+__device__ __forceinline__ float bfr(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+// One warp: RMSNorm (optional) + RoPE of one head `src` [D] -> dst (bf16).  Same arithmetic as
+// qk_norm_rope_store_kernel.
+__device__ __forceinline__ void norm_rope_head(const bf16* __restrict__ src, const float* __restrict__ w,
+                                               const float* __restrict__ inv_freq, int pos, int R, float eps, int has_norm,
+                                               bf16* dst, bf16* dst2, int lane) {
+  float inv = 1.f;
+  if (has_norm) {
+    float ss = 0.f;
+    for (int i = lane; i < D; i += 32) {
+      const float v = __bfloat162float(src[i]);
+      ss += v * v;
+    }
+    ss = warp_sum(ss);
+    inv = rsqrtf(ss / (float)D + eps);
+  }
+  const int half = R >> 1;
+  for (int j = lane; j < half; j += 32) {
+    float a = __bfloat162float(src[j]), b = __bfloat162float(src[j + half]);
+    if (has_norm) {
+      a = bfr(bfr(a * inv) * w[j]);
+      b = bfr(bfr(b * inv) * w[j + half]);
+    }
+    float sn, cs;
+    sincosf((float)pos * inv_freq[j], &sn, &cs);
+    cs = bfr(cs);
+    sn = bfr(sn);
+    const bf16 o1 = __float2bfloat16_rn(__fadd_rn(bfr(__fmul_rn(a, cs)), -bfr(__fmul_rn(b, sn))));
+    const bf16 o2 = __float2bfloat16_rn(__fadd_rn(bfr(__fmul_rn(b, cs)), bfr(__fmul_rn(a, sn))));
+    dst[j] = o1;
+    dst[j + half] = o2;
+    if (dst2) { dst2[j] = o1; dst2[j + half] = o2; }
+  }
+  for (int i = R + lane; i < D; i += 32) {
+    float a = __bfloat162float(src[i]);
+    if (has_norm) a = bfr(bfr(a * inv) * w[i]);
+    dst[i] = __float2bfloat16_rn(a);
+    if (dst2) dst2[i] = __float2bfloat16_rn(a);
+  }
+}
+
+struct Params {
+  const bf16* qkv; int qkv_stride;            // [rows, q | k | v]
+  const float* wq; const float* wk; const float* inv_freq;
+  const int* tok_slot; const int* tok_pos;
+  bf16* k_pages; bf16* v_pages;               // [pages, nKV, PAGE, D]
+  const int* page_table; int max_pages;
+  bf16* out;                                  // [rows, nH * D]
+  float* part_o; float* part_ml; int* tickets;  // [rows, nKV, S, G, D], [rows, nKV, S, G, 2], [rows * nKV]
+  int nKV; int n_splits; float scale; int window; int R; float eps; int has_norm; int write_kv;
+};
+
+__global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
+  extern __shared__ __align__(16) unsigned char smem[];
+  bf16* qs = reinterpret_cast<bf16*>(smem);                        // [16][KS], rows >= G zero
+  unsigned char* pipe = smem + Q_BYTES;
+  __shared__ int is_last;
+
+  const int n = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+  const int nH = p.nKV * G;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int g = lane >> 2, t = lane & 3;
+
+  pdl_launch_dependents();
+  pdl_wait();  // the projection that made qkv, and this step's token metadata, are complete
+
+  const int slot = p.tok_slot[n];
+  if (slot < 0) {  // padding row: defined zeros (written by split 0), no cache access, no ticket
+    if (split == 0)
+      for (int i = tid; i < G * D; i += THREADS) p.out[(size_t)n * nH * D + (size_t)kvh * G * D + i] = __float2bfloat16_rn(0.f);
+    return;
+  }
+  const int pos = p.tok_pos[n];
+  const int kv_hi = pos + 1;
+  const int kv_lo = p.window > 0 ? max(0, kv_hi - p.window) : 0;
+  const int first_page = kv_lo / PAGE, last_page = pos / PAGE;
+  const int n_pages = last_page - first_page + 1;
+  const int per_split = (n_pages + p.n_splits - 1) / p.n_splits;
+  const int pg_begin = first_page + split * per_split;
+  const int pg_end = min(pg_begin + per_split, last_page + 1);
+  const int* pt = p.page_table + (size_t)slot * p.max_pages;
+  const bf16* row = p.qkv + (size_t)n * p.qkv_stride;
+
+  // ---- each warp's first slices are requested before anything else is computed ----
+  bf16* stage = reinterpret_cast<bf16*>(pipe + (size_t)warp * WARP_STAGE_BYTES);  // [STAGES][K|V][SLICE][KS]
+  // slices of this block, in key order: slice index sl covers keys sl*16 .. sl*16+15
+  const int sl_begin = max(pg_begin * SPP, kv_lo / SLICE);
+  const int sl_end = min(pg_end * SPP, (kv_hi + SLICE - 1) / SLICE);
+  constexpr int CPR = D / 8;
+  // a lane copies 16-byte chunk (lane % CPL) of rows lane / CPL, lane / CPL + RPI, ...: fixed offsets
+  constexpr int CPL = CPR < 32 ? CPR : 32;        // chunks of one row handled side by side
+  constexpr int RPI = 32 / CPL;                   // rows per instruction
+  constexpr int CREP = CPR / CPL;                 // chunk repeats per row (head sizes above 256 elements: none)
+  const int lr = lane / CPL, lc = lane % CPL;
+  auto request = [&](int sl, int st) {
+    if (sl < sl_end) {
+      const int pg = sl / SPP;
+      const size_t base = (((size_t)pt[pg] * p.nKV + kvh) * PAGE + (size_t)(sl % SPP) * SLICE) * D;
+      const bf16* ksrc = p.k_pages + base + (size_t)lr * D + lc * 8;
+      const bf16* vsrc = p.v_pages + base + (size_t)lr * D + lc * 8;
+      bf16* kd = stage + (size_t)st * 2 * SLICE * KS + lr * KS + lc * 8;
+      bf16* vd = kd + SLICE * KS;
+#pragma unroll
+      for (int r = 0; r < SLICE; r += RPI)
+#pragma unroll
+        for (int c = 0; c < CREP; ++c) {
+          if ((SLICE % RPI == 0 && 32 % CPL == 0) || (r + lr < SLICE && lane < RPI * CPL)) {
+            cp_async16(kd + r * KS + c * CPL * 8, ksrc + (size_t)r * D + c * CPL * 8);
+            cp_async16(vd + r * KS + c * CPL * 8, vsrc + (size_t)r * D + c * CPL * 8);
+          }
+        }
+    }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int i = 0; i < STAGES - 1; ++i) request(sl_begin + warp + i * NWARP, i);
+
+  // ---- the row's queries; and, in the block that owns the last page, the new key and value ----
+  bf16* new_k = qs + 16 * KS;
+  bf16* new_v = new_k + KS;
+  for (int i = tid; i < (16 - G) * (D / 8); i += THREADS)  // zero the padding rows of Q
+    *reinterpret_cast<uint4*>(qs + (G + i / (D / 8)) * KS + (i % (D / 8)) * 8) = make_uint4(0, 0, 0, 0);
+  const bool owns_new = p.write_kv && last_page >= pg_begin && last_page < pg_end;
+  const int n_items = G + (owns_new ? 2 : 0);
+  for (int item = warp; item < n_items; item += NWARP) {
+    if (item < G) {
+      norm_rope_head(row + (size_t)(kvh * G + item) * D, p.wq, p.inv_freq, pos, p.R, p.eps, p.has_norm, qs + item * KS, nullptr, lane);
+    } else {
+      const size_t off = (((size_t)pt[last_page] * p.nKV + kvh) * PAGE + (pos % PAGE)) * D;
+      if (item == G) {
+        norm_rope_head(row + (size_t)(nH + kvh) * D, p.wk, p.inv_freq, pos, p.R, p.eps, p.has_norm, p.k_pages + off, new_k, lane);
+      } else {
+        const bf16* vsrc = row + (size_t)(nH + p.nKV + kvh) * D;
+        for (int i = lane; i < D; i += 32) {
+          const bf16 v = vsrc[i];
+          p.v_pages[off + i] = v;
+          new_v[i] = v;
+        }
+      }
+    }
+  }
+  __syncthreads();  // queries (and the new key and value) are in shared memory
+
+  // ---- each warp walks its own 16-key slices of the block's pages ----
+  float o_acc[DT][4];
+#pragma unroll
+  for (int j = 0; j < DT; ++j)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) o_acc[j][i] = 0.f;
+  float m_run[2] = {-INFINITY, -INFINITY};  // rows g and g+8 (heads), in log2 units
+  float l_run[2] = {0.f, 0.f};              // this thread's share of the row sums
+  const float scale_log2 = p.scale * 1.4426950408889634f;
+
+  int it = 0;
+  for (int sl = sl_begin + warp; sl < sl_end; sl += NWARP, ++it) {
+    const int st = it % STAGES;
+    request(sl + (STAGES - 1) * NWARP, (it + STAGES - 1) % STAGES);   // the next slice flies while this one is used
+    cp_async_wait<STAGES - 1>();
+    __syncwarp();
+    bf16* kst = stage + (size_t)st * 2 * SLICE * KS;
+    bf16* vst = kst + SLICE * KS;
+    if (owns_new && sl == pos / SLICE) {  // the staged copy of the token's own row may predate its write
+      const int r = pos % SLICE;
+      for (int i = lane; i < CPR; i += 32) {
+        *reinterpret_cast<uint4*>(kst + r * KS + i * 8) = *reinterpret_cast<const uint4*>(new_k + i * 8);
+        *reinterpret_cast<uint4*>(vst + r * KS + i * 8) = *reinterpret_cast<const uint4*>(new_v + i * 8);
+      }
+      __syncwarp();
+    }
+
+    // S = Q K^T: 16 (heads, padded) x 16 keys
+    float s[2][4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) s[j][i] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < KSTEPS; ++kk) {
+      unsigned a0, a1, a2, a3, b0, b1, b2, b3;
+      ldsm_x4(a0, a1, a2, a3, qs + (lane & 15) * KS + kk * 16 + (lane >> 4) * 8);
+      ldsm_x4(b0, b1, b2, b3, kst + ((lane & 7) + (lane >> 4) * 8) * KS + kk * 16 + ((lane >> 3) & 1) * 8);
+      mma16816(s[0], a0, a1, a2, a3, b0, b1);
+      mma16816(s[1], a0, a1, a2, a3, b2, b3);
+    }
+    // mask, online softmax (log2 domain); every slice visited holds at least one visible key
+    const int key0 = sl * SLICE;
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int kp = key0 + j * 8 + 2 * t + (i & 1);
+        const float v = (kp >= kv_lo && kp < kv_hi) ? s[j][i] * scale_log2 : -INFINITY;
+        s[j][i] = v;
+        if (i < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+      }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
+    const float mu0 = (mn0 == -INFINITY) ? 0.f : mn0, mu1 = (mn1 == -INFINITY) ? 0.f : mn1;
+    const float al0 = exp2f(m_run[0] - mu0), al1 = exp2f(m_run[1] - mu1);
+    m_run[0] = mn0;
+    m_run[1] = mn1;
+    float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      s[j][0] = exp2f(s[j][0] - mu0);
+      s[j][1] = exp2f(s[j][1] - mu0);
+      s[j][2] = exp2f(s[j][2] - mu1);
+      s[j][3] = exp2f(s[j][3] - mu1);
+      sum0 += s[j][0] + s[j][1];
+      sum1 += s[j][2] + s[j][3];
+    }
+    l_run[0] = l_run[0] * al0 + sum0;
+    l_run[1] = l_run[1] * al1 + sum1;
+#pragma unroll
+    for (int j = 0; j < DT; ++j) {
+      o_acc[j][0] *= al0;
+      o_acc[j][1] *= al0;
+      o_acc[j][2] *= al1;
+      o_acc[j][3] *= al1;
+    }
+    // O += P V (one k16 step: the slice's 16 keys)
+    const unsigned pa0 = pack_bf16(s[0][0], s[0][1]), pa1 = pack_bf16(s[0][2], s[0][3]);
+    const unsigned pa2 = pack_bf16(s[1][0], s[1][1]), pa3 = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+    for (int j = 0; j < DT; j += 2) {
+      unsigned b0, b1, b2, b3;
+      ldsm_x4_t(b0, b1, b2, b3, vst + ((lane & 7) + ((lane >> 3) & 1) * 8) * KS + j * 8 + (lane >> 4) * 8);
+      mma16816(o_acc[j], pa0, pa1, pa2, pa3, b0, b1);
+      mma16816(o_acc[j + 1], pa0, pa1, pa2, pa3, b2, b3);
+    }
+    __syncwarp();  // the stage may be refilled by the request two iterations on
+  }
+  cp_async_wait<0>();
+  __syncthreads();  // every warp is done with its stages: they become the combine buffers
+
+  // ---- combine the warps of this block ----
+  float* wm = reinterpret_cast<float*>(pipe);          // [NWARP][16]
+  float* wl = wm + NWARP * 16;                         // [NWARP][16]
+  float* wacc = wl + NWARP * 16;                       // [NWARP][G][D]
+  float l0 = l_run[0], l1 = l_run[1];
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+  if (t == 0) {
+    wm[warp * 16 + g] = m_run[0]; wl[warp * 16 + g] = l0;
+    wm[warp * 16 + g + 8] = m_run[1]; wl[warp * 16 + g + 8] = l1;
+  }
+#pragma unroll
+  for (int j = 0; j < DT; ++j) {
+    const int d = j * 8 + 2 * t;
+    if (g < G) { wacc[(warp * G + g) * D + d] = o_acc[j][0]; wacc[(warp * G + g) * D + d + 1] = o_acc[j][1]; }
+    if (g + 8 < G) { wacc[(warp * G + g + 8) * D + d] = o_acc[j][2]; wacc[(warp * G + g + 8) * D + d + 1] = o_acc[j][3]; }
+  }
+  __syncthreads();
+  const size_t pidx = ((size_t)n * p.nKV + kvh) * p.n_splits + split;
+  for (int i = tid; i < G * D; i += THREADS) {
+    const int h = i / D, d = i % D;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < NWARP; ++w) mx = fmaxf(mx, wm[w * 16 + h]);
+    float num = 0.f, den = 0.f;
+#pragma unroll
+    for (int w = 0; w < NWARP; ++w) {
+      const float m = wm[w * 16 + h];
+      if (m == -INFINITY) continue;
+      const float sc = exp2f(m - mx);
+      num += sc * wacc[(w * G + h) * D + d];
+      den += sc * wl[w * 16 + h];
+    }
+    if (p.n_splits == 1) {
+      p.out[((size_t)n * nH + kvh * G + h) * D + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+    } else {
+      p.part_o[(pidx * G + h) * D + d] = num;  // relative to mx
+      if (d == 0) { p.part_ml[(pidx * G + h) * 2] = mx; p.part_ml[(pidx * G + h) * 2 + 1] = den; }
+    }
+  }
+  if (p.n_splits == 1) return;
+
+  // ---- the block that draws the last ticket combines all splits, in split order ----
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int t = atomicAdd(&p.tickets[n * p.nKV + kvh], 1);
+    is_last = (t == p.n_splits - 1);
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  // The combine reads are independent of each other: all (m, l) pairs first, then one weight per
+  // (split, head), then every output element sums its S partials with the loads in flight together.
+  const size_t pbase = ((size_t)n * p.nKV + kvh) * p.n_splits;
+  float* cm = reinterpret_cast<float*>(pipe);        // [S][G] maxima (the stages are free again)
+  float* cl = cm + p.n_splits * G;                   // [S][G] sums
+  float* cw = cl + p.n_splits * G;                   // [S][G] weights exp2(m - max) / total
+  __syncthreads();
+  for (int i = tid; i < p.n_splits * G; i += THREADS) {
+    cm[i] = __ldcg(&p.part_ml[(pbase * G + i) * 2]);
+    cl[i] = __ldcg(&p.part_ml[(pbase * G + i) * 2 + 1]);
+  }
+  __syncthreads();
+  if (tid < G) {
+    float mx = -INFINITY;
+    for (int s2 = 0; s2 < p.n_splits; ++s2) mx = fmaxf(mx, cm[s2 * G + tid]);
+    float den = 0.f;
+    for (int s2 = 0; s2 < p.n_splits; ++s2) {
+      const float m = cm[s2 * G + tid];
+      const float sc = m == -INFINITY ? 0.f : exp2f(m - mx);  // maxima are kept in log2 units
+      cw[s2 * G + tid] = sc;
+      den += sc * cl[s2 * G + tid];
+    }
+    const float inv = den > 0.f ? 1.f / den : 0.f;
+    for (int s2 = 0; s2 < p.n_splits; ++s2) cw[s2 * G + tid] *= inv;
+  }
+  __syncthreads();
+  for (int i = tid; i < G * D; i += THREADS) {
+    const int h = i / D, d = i % D;
+    float num = 0.f;
+#pragma unroll 8
+    for (int s2 = 0; s2 < p.n_splits; ++s2) num += cw[s2 * G + h] * __ldcg(&p.part_o[((pbase + s2) * G + h) * D + d]);
+    p.out[((size_t)n * nH + kvh * G + h) * D + d] = __float2bfloat16_rn(num);
+  }
+  if (tid == 0) p.tickets[n * p.nKV + kvh] = 0;  // ready for the next launch
+}
+}  // namespace
+
+DRYFT_API int dryft_attn_decode_head_dim() { return D; }
+DRYFT_API int dryft_attn_decode_group() { return G; }
+
+DRYFT_API int dryft_attn_decode(const void* qkv, int qkv_stride, const float* wq, const float* wk, const float* inv_freq,
+                                const int* tok_slot, const int* tok_pos, void* k_pages, void* v_pages,
+                                const int* page_table, int max_pages, void* out, float* part_o, float* part_ml,
+                                int* tickets, int n_rows, int nKV, int n_splits, float scale, int window, int R, float eps,
+                                int has_norm, int write_kv, int pdl, cudaStream_t st) {
+  if (n_rows <= 0) return 0;
+  if (n_splits < 1 || nKV < 1 || nKV > 65535 || n_splits > 64 || (R & 1) || R > D || R < 0) return DRYFT_ERR_UNSUPPORTED;
+  if (n_splits > 1 && (!part_o || !part_ml || !tickets)) return DRYFT_ERR_UNSUPPORTED;
+  Params p;
+  p.qkv = (const bf16*)qkv; p.qkv_stride = qkv_stride; p.wq = wq; p.wk = wk; p.inv_freq = inv_freq;
+  p.tok_slot = tok_slot; p.tok_pos = tok_pos; p.k_pages = (bf16*)k_pages; p.v_pages = (bf16*)v_pages;
+  p.page_table = page_table; p.max_pages = max_pages; p.out = (bf16*)out; p.part_o = part_o; p.part_ml = part_ml;
+  p.tickets = tickets; p.nKV = nKV; p.n_splits = n_splits; p.scale = scale; p.window = window; p.R = R; p.eps = eps;
+  p.has_norm = has_norm; p.write_kv = write_kv;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(n_rows, nKV, n_splits);
+  cfg.blockDim = dim3(THREADS);
+  static bool attr_set = false;  // set by the first (eager) launch, outside any stream capture
+  if (SMEM_BYTES > 48 * 1024 && !attr_set) {
+    cudaError_t ea = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    if (ea != cudaSuccess) return (int)ea;
+    attr_set = true;
+  }
+  cfg.dynamicSmemBytes = SMEM_BYTES;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, attn_decode_kernel, p);
+  if (e != cudaSuccess) return (int)e;
+  return launch_status();
+}

@@ -33,7 +33,7 @@ class Stepper:
         self.cache = cache
         self.rt = rt
         self.cuda_graphs = cuda_graphs
-        self._graphs: Dict[int, "_DecodeGraph"] = {}
+        self._graphs: Dict[tuple, "_DecodeGraph"] = {}
         self._pinned: Optional[torch.Tensor] = None
         self._upload_event: Optional[torch.cuda.Event] = None
         self.last_decode_slots: Optional[torch.Tensor] = None
@@ -101,8 +101,8 @@ class Stepper:
         tok_slot, tok_pos = meta[:N], meta[N:]
         K.step_meta(d_cu, d_slot, self.cache.seq_len, tok_slot, tok_pos, N, B)
         ctx = StepContext(n_tokens=N, n_seqs=B, tokens=d_tokens, cu_q=d_cu, seq_slot=d_slot, tok_slot=tok_slot,
-                          tok_pos=tok_pos, decode=decode, tile_tok0=d_t0 if T else None, tile_rows=d_tn if T else None,
-                          n_tiles=T, tile_size=PREFILL_TILE)
+                          tok_pos=tok_pos, decode=decode, max_kv=max(st + q for st, q in zip(starts, q_lens)),
+                          tile_tok0=d_t0 if T else None, tile_rows=d_tn if T else None, n_tiles=T, tile_size=PREFILL_TILE)
         logits = self.model.forward(ctx, self.cache, d_rows if W else None, W)
         K.step_advance(d_cu, d_slot, self.cache.seq_len, B)
         for s, q in zip(slots, q_lens):
@@ -137,10 +137,13 @@ class Stepper:
             self.cache.reserve(s, 1)
         self.cache.flush()
         bucket = _bucket(B)
-        g = self._graphs.get(bucket)
+        # one graph per (batch size, context bucket): the context bucket only decides how the decode
+        # attention splits its keys across blocks (the reference buckets lengths too, config.py:169-170)
+        kv_bucket = _kv_bucket(max(self.cache.len_host[s] for s in slots) + 1)
+        g = self._graphs.get((bucket, kv_bucket))
         if g is None:
-            g = _DecodeGraph(self, bucket)
-            self._graphs[bucket] = g
+            g = _DecodeGraph(self, bucket, kv_bucket)
+            self._graphs[(bucket, kv_bucket)] = g
         logits = g.run(slots)
         for s in slots:
             self.cache.advanced(s, 1)
@@ -158,12 +161,22 @@ def _bucket(b: int) -> int:
     return (b + 7) // 8 * 8
 
 
-class _DecodeGraph:
-    """Static buffers and (optionally) a captured graph of one decode step at a fixed batch size."""
+def _kv_bucket(n: int) -> int:
+    """Context lengths are bucketed to 1024, 2048, 4096, ..."""
+    b = 1024
+    while b < n:
+        b *= 2
+    return b
 
-    def __init__(self, stepper: Stepper, bucket: int):
+
+class _DecodeGraph:
+    """Static buffers and (optionally) a captured graph of one decode step at a fixed batch size and
+    context bucket."""
+
+    def __init__(self, stepper: Stepper, bucket: int, kv_bucket: int):
         self.st = stepper
         self.bucket = bucket
+        self.kv_bucket = kv_bucket
         dev = stepper.rt.device
         # pinned staging for the per-step slot list: a ring, so the host may run several steps ahead
         self.ring = [torch.full((bucket,), -1, dtype=torch.int32).pin_memory() for _ in range(8)]
@@ -185,7 +198,8 @@ class _DecodeGraph:
         K.tokens_from_state(self.seq_slot, st.cache.last_token, self.tokens, self.bucket)
         K.step_meta(self.cu_q, self.seq_slot, st.cache.seq_len, self.tok_slot, self.tok_pos, self.bucket, self.bucket)
         ctx = StepContext(n_tokens=self.bucket, n_seqs=self.bucket, tokens=self.tokens, cu_q=self.cu_q,
-                          seq_slot=self.seq_slot, tok_slot=self.tok_slot, tok_pos=self.tok_pos, decode=True)
+                          seq_slot=self.seq_slot, tok_slot=self.tok_slot, tok_pos=self.tok_pos, decode=True,
+                          max_kv=self.kv_bucket)
         logits = st.model.forward(ctx, st.cache, self.rows, self.bucket, all_rows=True)
         K.step_advance(self.cu_q, self.seq_slot, st.cache.seq_len, self.bucket)
         return logits

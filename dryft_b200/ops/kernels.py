@@ -94,6 +94,44 @@ def attention_rows_lib(head_dim: int, group: int, page: int) -> ctypes.CDLL:
         return lib
 
 
+def attention_decode_supported(head_dim: int, group: int) -> bool:
+    """Whether the one-launch decode attention exists for these sizes (the query heads of a kv head
+    form one 16-row tensor-core operand)."""
+    return head_dim > 0 and head_dim % 16 == 0 and head_dim <= 256 and 1 <= group <= 16
+
+
+def attention_decode_lib(head_dim: int, group: int, page: int) -> ctypes.CDLL:
+    """The fused decode attention (RoPE + cache write + split attention + combine, bfloat16)."""
+    if not attention_decode_supported(head_dim, group):
+        raise KernelError(f"fused decode attention does not take head_dim={head_dim} with {group} query heads per kv head")
+    key = ("decode", head_dim, group, page)
+    with _lock:
+        lib = _variants.get(key)
+        if lib is None:
+            path = build.build_library("attn_decode", ("attn_decode.cu",),
+                                       {"DRYFT_HEAD_DIM": head_dim, "DRYFT_GROUP": group, "DRYFT_PAGE": page})
+            lib = _load(path)
+            lib.dryft_attn_decode.argtypes = [_p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _f, _i,
+                                              _i, _f, _i, _i, _i, _p]
+            lib.dryft_attn_decode.restype = _i
+            _variants[key] = lib
+        return lib
+
+
+_tickets: Dict[int, torch.Tensor] = {}
+
+
+def tickets(device: torch.device, n: int) -> torch.Tensor:
+    """Zeroed int32 counters the decode attention's blocks draw tickets from; every launch leaves
+    them zero again, so one buffer per device serves all layers."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    t = _tickets.get(idx)
+    if t is None or t.numel() < n:
+        t = torch.zeros(max(n, 1 << 16), dtype=torch.int32, device=torch.device("cuda", idx))
+        _tickets[idx] = t
+    return t
+
+
 def attention_prefill_lib(head_dim: int, group: int, page: int) -> ctypes.CDLL:
     """The tensor-core prefill attention kernel (bfloat16) compiled for these sizes."""
     if head_dim <= 0 or head_dim % 16 or head_dim > 256:
@@ -308,6 +346,45 @@ def attn_rows(q, k_pages, v_pages, page_table, tok_slot, tok_pos, out, scale: fl
                             _ptr(tok_slot), _ptr(tok_pos), _ptr(out), _ptr(part_o), _ptr(part_ml), n, n_kv, n_splits,
                             float(scale), int(window or 0), _stream()), f"attn_rows (head_dim {head_dim})",
         n_kernels=2 if n_splits > 1 else 1)
+
+
+def attn_decode(qkv, q_norm_w, k_norm_w, inv_freq, tok_slot, tok_pos, k_pages, v_pages, page_table, out,
+                n_heads: int, n_kv_heads: int, head_dim: int, rotary_dim: int, eps: float, scale: float,
+                window: Optional[int], n_splits: int, part_o=None, part_ml=None, write_kv: bool = True, pdl: bool = False) -> None:
+    """One launch for a decode step's attention (bfloat16): per-head q/k norm + RoPE of each row's new
+    token, its K/V written into the cache, attention of its query heads over the cache, splits combined."""
+    n = qkv.shape[0]
+    width = (n_heads + (2 * n_kv_heads if write_kv else 0)) * head_dim
+    _need(qkv, "qkv", torch.bfloat16, (n, width))
+    has_norm = q_norm_w is not None
+    if has_norm:
+        _need(q_norm_w, "q_norm weight", torch.float32, (head_dim,))
+        _need(k_norm_w, "k_norm weight", torch.float32, (head_dim,))
+    if rotary_dim:
+        _need(inv_freq, "inv_freq", torch.float32, (rotary_dim // 2,))
+    page = k_pages.shape[2]
+    _need(k_pages, "k_pages", torch.bfloat16, (None, n_kv_heads, page, head_dim))
+    _need(v_pages, "v_pages", torch.bfloat16, tuple(k_pages.shape))
+    for t, nm in ((page_table, "page_table"), (tok_slot, "tok_slot"), (tok_pos, "tok_pos")):
+        _need(t, nm, torch.int32)
+    if tok_slot.numel() < n or tok_pos.numel() < n:
+        raise KernelError("attn_decode: token index arrays shorter than the batch")
+    _need(out, "attention output", torch.bfloat16, (n, n_heads * head_dim))
+    if n_heads % n_kv_heads:
+        raise KernelError(f"attn_decode: {n_heads} query heads are not a multiple of {n_kv_heads} kv heads")
+    tk = None
+    if n_splits > 1:
+        _need(part_o, "part_o", torch.float32)
+        _need(part_ml, "part_ml", torch.float32)
+        if part_o.numel() < n * n_heads * n_splits * head_dim or part_ml.numel() < n * n_heads * n_splits * 2:
+            raise KernelError("attn_decode: partial buffers too small for the split count")
+        tk = tickets(qkv.device, n * n_kv_heads)
+    lib = attention_decode_lib(head_dim, n_heads // n_kv_heads, page)
+    _ok(lib.dryft_attn_decode(_ptr(qkv), width, _ptr(q_norm_w), _ptr(k_norm_w), _ptr(inv_freq), _ptr(tok_slot), _ptr(tok_pos),
+                              _ptr(k_pages), _ptr(v_pages), _ptr(page_table), page_table.shape[1], _ptr(out), _ptr(part_o),
+                              _ptr(part_ml), _ptr(tk), n, n_kv_heads, n_splits, float(scale), int(window or 0),
+                              int(rotary_dim), float(eps), int(has_norm), int(write_kv), int(pdl), _stream()),
+        f"attn_decode (head_dim {head_dim})")
 
 
 def attn_prefill(q, k_pages, v_pages, page_table, tile_tok0, tile_rows, tok_slot, tok_pos, out, n_tiles: int,

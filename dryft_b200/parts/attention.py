@@ -75,8 +75,11 @@ class Attention:
         # build (or find) the kernels this head shape needs now, not at the first step
         K.attention_rows_lib(self.head_dim, self.group, rt.page_size)
         self.use_prefill_kernel = rt.is_bf16
+        self.use_decode_kernel = rt.is_bf16 and rt.fuse_decode and K.attention_decode_supported(self.head_dim, self.group)
         if self.use_prefill_kernel:
             K.attention_prefill_lib(self.head_dim, self.group, rt.page_size)
+        if self.use_decode_kernel:
+            K.attention_decode_lib(self.head_dim, self.group, rt.page_size)
 
     def kv_need(self) -> Optional[KVNeed]:
         return KVNeed(self.n_kv, self.head_dim, self.window)
@@ -89,6 +92,13 @@ class Attention:
         two programs per SM, ``kernels/attn_decode.py:143-149``)."""
         want = math.ceil(2 * self.rt.sm_count / max(1, n_rows * self.n_kv))
         return max(1, min(32, want))
+
+    @staticmethod
+    def _decode_splits(max_kv: int) -> int:
+        """Splits of the one-launch decode attention: a block's 8 warps share up to 1,024 keys through
+        shared memory for nothing, and combining splits across blocks costs a few round trips through
+        memory, so keys are only split across blocks when sequences are longer than that."""
+        return max(1, min(32, (max(1, max_kv) + 1023) // 1024))
 
     def can_fuse(self, n_rows: int, norm) -> bool:
         """Few rows, bfloat16 everywhere, widths the weight-streaming product takes."""
@@ -122,6 +132,18 @@ class Attention:
         n = qkv.shape[0]
         dev = qkv.device
         h = qkv
+        if ctx.decode and self.use_decode_kernel:
+            # one launch: q/k norm + RoPE + cache write + split attention + combine
+            o = torch.empty((n, self.q_dim), dtype=h.dtype, device=dev)
+            s = self._decode_splits(ctx.max_kv)
+            part_o = part_ml = None
+            if s > 1:
+                part_o = torch.empty((n, self.n_heads, s, self.head_dim), dtype=torch.float32, device=dev)
+                part_ml = torch.empty((n, self.n_heads, s, 2), dtype=torch.float32, device=dev)
+            K.attn_decode(qkv, self.q_norm_w, self.k_norm_w, self.position.inv_freq, ctx.tok_slot, ctx.tok_pos, cache.k, cache.v,
+                          cache.page_table, o, self.n_heads, self.n_kv, self.head_dim, self.position.rotary_dim, self.qk_eps,
+                          self.scale, self.window, s, part_o, part_ml, write_kv=owns_cache, pdl=self.rt.pdl)
+            return o
         q = torch.empty((n, self.n_heads, self.head_dim), dtype=h.dtype, device=dev)
         K.qk_norm_rope_store(qkv, self.q_norm_w, self.k_norm_w, self.position.inv_freq, ctx.tok_slot, ctx.tok_pos, q,
                              cache.k, cache.v, cache.page_table, self.n_heads, self.n_kv, self.head_dim,

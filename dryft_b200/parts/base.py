@@ -71,6 +71,7 @@ class StepContext:
     tok_slot: torch.Tensor        # int32 [n_tokens]
     tok_pos: torch.Tensor         # int32 [n_tokens]: absolute position of each token
     decode: bool                  # host: every sequence brings exactly one token
+    max_kv: int = 0               # host: no sequence is longer than this after the step (a bound, may be loose)
     tile_tok0: Optional[torch.Tensor] = None   # int32 [n_tiles]: first packed token of a query tile
     tile_rows: Optional[torch.Tensor] = None   # int32 [n_tiles]: tokens in the tile (<= tile_size)
     n_tiles: int = 0

@@ -329,6 +329,71 @@ def test_attn_rows(dtype, n_heads, n_kv, d, window):
         torch.testing.assert_close(out.cpu().float(), ref, rtol=rt, atol=at)
 
 
+@pytest.mark.parametrize("n_heads,n_kv,d,rot", [(4, 2, 16, 16), (6, 2, 48, 48), (8, 2, 128, 128), (5, 5, 64, 32), (16, 1, 32, 32)])
+@pytest.mark.parametrize("window", [None, 70])
+def test_attn_decode_fused(n_heads, n_kv, d, rot, window):
+    """The one-launch decode attention against the plain parts: q/k norm + RoPE of the new token, its
+    K/V written into the cache (and nothing else), attention over old keys plus the new one, for
+    every split count; tickets are left at zero."""
+    k = K()
+    dtype = torch.bfloat16
+    page, theta, eps = 64, 1e4, 1e-5
+    scale = 1.0 / math.sqrt(d)
+    lens = {0: 0, 1: 63, 2: 64, 3: 200, 4: 129}  # tokens already cached; the new token goes at this position
+    seqs = {s: (torch.randn(L + 1, n_kv, d).to(dtype), torch.randn(L + 1, n_kv, d).to(dtype)) for s, L in lens.items()}
+    rows = [(0, 0), (1, 63), (-1, 0), (2, 64), (3, 200), (4, 129)]
+    n = len(rows)
+    width = (n_heads + 2 * n_kv) * d
+    qkv = (torch.randn(n, width) * 2).to(dtype)
+    wq = (1 + 0.1 * torch.randn(d)).to(dtype).float()
+    wk = (1 + 0.1 * torch.randn(d)).to(dtype).float()
+    inv_freq = 1.0 / (theta ** (torch.arange(0, rot, 2, dtype=torch.int64).float() / rot))
+    # plain: rotate q and the new k, put new k/v at the row's position, attend
+    pos_t = torch.tensor([r[1] for r in rows])
+    cos, sin = P.rope_cos_sin(pos_t, rot, theta, dtype)
+    q = qkv[:, :n_heads * d].view(n, n_heads, d)
+    kn = qkv[:, n_heads * d:(n_heads + n_kv) * d].view(n, n_kv, d)
+    vn = qkv[:, (n_heads + n_kv) * d:].view(n, n_kv, d)
+    rot_part = lambda x: torch.cat((P.apply_rope(x[..., :rot], cos, sin), x[..., rot:]), dim=-1)
+    q_r = rot_part(P.rmsnorm(q, wq, eps))
+    k_r = rot_part(P.rmsnorm(kn, wk, eps))
+    refs = []
+    for i, (s, pos) in enumerate(rows):
+        if s < 0:
+            refs.append(torch.zeros(n_heads * d))
+            continue
+        kseq, vseq = seqs[s][0].clone(), seqs[s][1].clone()
+        kseq[pos], vseq[pos] = k_r[i], vn[i]
+        refs.append(_attn_ref(q_r[i], kseq, vseq, pos, scale, window))
+    ref = torch.stack(refs)
+    for splits in (1, 2, 7):
+        old = {s: (kv[0][:lens[s]], kv[1][:lens[s]]) for s, kv in seqs.items()}
+        # pages for L+1 tokens, only L filled; the rest is a canary the kernel must not touch
+        kc, vc, pt = _fill_cache({s: (torch.cat([kv[0], torch.full((1, n_kv, d), 55.0).to(dtype)]),
+                                      torch.cat([kv[1], torch.full((1, n_kv, d), 55.0).to(dtype)])) for s, kv in old.items()},
+                                 n_kv, d, page, dtype, n_pages=16, max_pages=5, slots=6, scatter_seed=splits)
+        kc0, vc0 = kc.clone(), vc.clone()
+        out = torch.full((n, n_heads * d), 9.0, device=DEV, dtype=dtype)
+        po = torch.empty(n, n_heads, splits, d, device=DEV) if splits > 1 else None
+        pm = torch.empty(n, n_heads, splits, 2, device=DEV) if splits > 1 else None
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+        k.attn_decode(qkv.to(DEV), wq.to(DEV), wk.to(DEV), inv_freq.to(DEV), i32([r[0] for r in rows]), i32([r[1] for r in rows]),
+                      kc, vc, pt, out, n_heads, n_kv, d, rot, eps, scale, window, splits, po, pm)
+        assert torch.isfinite(out.float()).all()
+        torch.testing.assert_close(out.cpu().float(), ref, rtol=2e-2, atol=2e-2)
+        changed_k = (kc != kc0).any(dim=-1)
+        changed_v = (vc != vc0).any(dim=-1)
+        assert int(changed_k.sum()) == 5 * n_kv and int(changed_v.sum()) == 5 * n_kv  # one row per live token and kv head
+        for i, (s, pos) in enumerate(rows):
+            if s < 0:
+                continue
+            pg = int(pt[s, pos // page])
+            torch.testing.assert_close(kc[pg, :, pos % page].cpu().float(), k_r[i].float(), rtol=2e-2, atol=2e-2)
+            assert torch.equal(vc[pg, :, pos % page].cpu(), vn[i])
+        if splits > 1:
+            assert int(k.tickets(torch.device(DEV, 0), 1).abs().sum()) == 0
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_attn_rows_far_key_stands_out(dtype):
     """One key among hundreds is made to dominate (query and that key scaled so its score stands out);

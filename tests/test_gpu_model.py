@@ -349,7 +349,7 @@ def test_parts_alone(dtype):
         cu, tok_slot, tok_pos = i32([0, 13, 21]), torch.empty(21, dtype=torch.int32, device=dev), torch.empty(21, dtype=torch.int32, device=dev)
         K.step_meta(cu, i32(slots), cache.seq_len, tok_slot, tok_pos, 21, 2)
         ctx = StepContext(n_tokens=21, n_seqs=2, tokens=i32([0] * 21), cu_q=cu, seq_slot=i32(slots), tok_slot=tok_slot,
-                          tok_pos=tok_pos, decode=False, tile_tok0=i32([0, 13]), tile_rows=i32([13, 8]), n_tiles=2, tile_size=64)
+                          tok_pos=tok_pos, decode=False, max_kv=13, tile_tok0=i32([0, 13]), tile_rows=i32([13, 8]), n_tiles=2, tile_size=64)
         got = mixer.forward(x, ctx, cache.entry(0), None, True).cpu().float()
         refs = []
         for lo, n in ((0, 13), (13, 8)):
