@@ -1,0 +1,309 @@
+// Decode matrix product for one K, fixed at compile time (-DDRYFT_K, a multiple of 256): the same
+// operation, fusions and launch overlap as csrc/gemm_small_m.cu, but with every loop over k unrolled
+// and every offset an immediate, so that an instruction moves as many bytes as it can.  It is what a
+// model's decode step uses when its widths allow; gemm_small_m.cu remains the general form.
+//
+//   C[M,N] = A[M,K] * W[N,K]^T,  M <= 8 or <= 16,  bfloat16 operands, 32-bit accumulation,
+//   every weight byte read from HBM exactly once (hari495/dryft: cuBLAS via F.linear,
+//   engine/dryft_qwen3/model.py:237,258,260,261).
+//   norm prologue (kernels/rmsnorm.py:21-39), residual epilogue with sums of squares for the next
+//   norm (rmsnorm.py:34), SiLU*mul epilogue (kernels/silu_mul.py:29-32; weights.py:98-100).
+//
+// A block of 8 warps takes 16 rows of W at a time; blocks are persistent, at most two per SM, each
+// walking over every grid-th tile.  The warps split K into 8 equal ranges.  A warp requests its whole
+// share of the tile's 16 rows at once — K/128 16-byte loads per thread that bypass L1, all in flight
+// together — then feeds them to mma.sync.m16n8k16 with W as the 16 x 16 operand and 8 batch rows as
+// the 16 x 8 operand (the k index permuted identically in both operands, so that a thread's fragment
+// is one contiguous 16-byte piece).  While a warp consumes, the other fifteen on the SM have their
+// requests in flight.  With the norm prologue the normalised activations are made once per block and
+// stay in shared memory; otherwise they are read through L1.  The 8 partial sums are added in warp
+// order through shared memory: a row's result depends neither on the other rows nor on M.
+//
+// The kernel may be launched as a programmatic dependent of the launch before it: it requests its
+// first weights, which depend on nothing, and only then waits for the earlier grid.
+// No block waits on another block of its grid; there is no spin in this file.
+#include "common.cuh"
+
+#if !defined(DRYFT_K)
+#error "compile with -DDRYFT_K=<inner size, a multiple of 256>"
+#endif
+
+namespace {
+typedef __nv_bfloat16 bf16;
+constexpr int K = DRYFT_K;
+static_assert(K % 256 == 0, "this kernel takes inner sizes that are multiples of 256");
+constexpr int WARPS = 8;
+constexpr int THREADS = WARPS * 32;
+constexpr int ROWS = 16;
+constexpr int SPW = K / 32 / WARPS;           // 32-wide k steps per warp
+constexpr int CHUNK = SPW <= 10 ? SPW : 10;     // steps a warp requests together (the last chunk may be shorter)
+constexpr int N_CHUNKS = (SPW + CHUNK - 1) / CHUNK;
+constexpr int SS_STRIDE = 64;
+constexpr int KA = K + ((64 - (K * 2) % 128 + 128) % 128) / 2;  // resident row stride: bytes = 64 mod 128
+
+enum Mode { STORE_BF16 = 0, STORE_F32 = 1, RESIDUAL = 2, SILU = 3 };
+
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void mma16816(float (&c)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float bfr(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <int MB, int MODE, bool NORM>
+__global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
+    const bf16* __restrict__ A, int lda, const bf16* __restrict__ W, void* C, int ldc, int M, int N,
+    const float* __restrict__ norm_w, const float* __restrict__ ss_in, int ss_parts, float eps, float* __restrict__ ss_out) {
+  constexpr int MP = 8 * MB;
+  constexpr int RED = WARPS * ROWS * (MP + 1);
+  extern __shared__ __align__(16) unsigned char smem[];
+  // two buffers of [WARPS][ROWS][MP + 1] partial sums, 64 floats of inv, then the resident activations
+  float* red_base = reinterpret_cast<float*>(smem);
+  float* inv_s = red_base + 2 * RED;
+  bf16* a_res = reinterpret_cast<bf16*>(inv_s + SS_STRIDE);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+  const int g = lane >> 2, t = lane & 3;
+  constexpr int TILE_N = MODE == SILU ? 8 : ROWS;
+  const int n_tiles = (N + TILE_N - 1) / TILE_N;
+  const int k_warp = warp * SPW * 32 + t * 8;   // this thread's first k
+
+  pdl_launch_dependents();
+
+  uint4 wa[CHUNK], wb[CHUNK];
+  const uint4 zero = make_uint4(0, 0, 0, 0);
+  // this thread's two weight rows of a tile (tile rows g and g+8; SILU: gate row and matching up row)
+  auto rows_of = [&](int tile, const bf16*& w0, const bf16*& w1) {
+    const int n0 = tile * TILE_N;
+    int r0, r1;
+    bool ok0, ok1;
+    if (MODE == SILU) { r0 = n0 + g; r1 = N + n0 + g; ok0 = ok1 = n0 + g < N; }
+    else { r0 = n0 + g; r1 = n0 + g + 8; ok0 = r0 < N; ok1 = r1 < N; }
+    w0 = ok0 ? W + (size_t)r0 * K + k_warp : nullptr;
+    w1 = ok1 ? W + (size_t)r1 * K + k_warp : nullptr;
+  };
+  auto request = [&](const bf16* w0, const bf16* w1, const int chunk) {
+#pragma unroll
+    for (int u = 0; u < CHUNK; ++u) {
+      if (chunk * CHUNK + u < SPW) {  // folds away: both are constants once unrolled
+        wa[u] = w0 ? ld_stream(w0 + (chunk * CHUNK + u) * 32) : zero;
+        wb[u] = w1 ? ld_stream(w1 + (chunk * CHUNK + u) * 32) : zero;
+      }
+    }
+  };
+  int tile = blockIdx.x;
+  const bf16 *w0 = nullptr, *w1 = nullptr;
+  if (tile < n_tiles) {
+    rows_of(tile, w0, w1);
+    request(w0, w1, 0);  // weights depend on no earlier launch
+  }
+
+  pdl_wait();  // from here on, what earlier launches wrote (activations, sums of squares) is visible
+
+  if (NORM) {
+    // inv[m] = rsqrt(mean(x[m]^2) + eps): warp m adds the blocks of sums of squares in a fixed order;
+    // then the normalised rows a[m,k] = T(T(x[m,k] * inv[m]) * w[k]) go to shared memory once per block
+    for (int m = warp; m < MP; m += WARPS) {
+      float s = 0.f;
+      if (m < M)
+        for (int p = lane; p < ss_parts; p += 32) s += ss_in[(size_t)p * SS_STRIDE + m];
+      s = warp_sum(s);
+      if (lane == 0) inv_s[m] = rsqrtf(s / (float)K + eps);
+    }
+    __syncthreads();
+    constexpr int CHUNKS = K / 8;
+#pragma unroll 4
+    for (int i = tid; i < MP * CHUNKS; i += THREADS) {
+      const int m = i / CHUNKS, c = i - m * CHUNKS;
+      uint4 out = zero;
+      if (m < M) {
+        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(A + (size_t)m * lda + c * 8));
+        const float4 wv0 = __ldg(reinterpret_cast<const float4*>(norm_w + c * 8));
+        const float4 wv1 = __ldg(reinterpret_cast<const float4*>(norm_w + c * 8 + 4));
+        const float wv[8] = {wv0.x, wv0.y, wv0.z, wv0.w, wv1.x, wv1.y, wv1.z, wv1.w};
+        const bf16* e = reinterpret_cast<const bf16*>(&raw);
+        const float inv = inv_s[m];
+        __align__(16) bf16 o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16_rn(bfr(__bfloat162float(e[j]) * inv) * wv[j]);
+        out = *reinterpret_cast<const uint4*>(o);
+      }
+      *reinterpret_cast<uint4*>(a_res + (size_t)m * KA + c * 8) = out;
+    }
+    __syncthreads();
+  }
+  // this thread's activation fragments: batch row mb*8 + g, k as for the weights
+  const bf16* a_frag = NORM ? a_res + (size_t)g * KA + k_warp : A + (size_t)g * lda + k_warp;
+  const size_t a_mb = NORM ? (size_t)8 * KA : (size_t)8 * lda;
+
+  int buf = 0;
+  for (; tile < n_tiles; tile += gridDim.x) {
+    float acc[MB][4];
+#pragma unroll
+    for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[mb][i] = 0.f;
+
+#pragma unroll
+    for (int chunk = 0; chunk < N_CHUNKS; ++chunk) {
+      if (chunk > 0) request(w0, w1, chunk);
+#pragma unroll
+      for (int u = 0; u < CHUNK; ++u) {
+        if (chunk * CHUNK + u >= SPW) continue;
+#pragma unroll
+        for (int mb = 0; mb < MB; ++mb) {
+          uint4 a = zero;
+          if (NORM) a = *reinterpret_cast<const uint4*>(a_frag + mb * a_mb + (chunk * CHUNK + u) * 32);
+          else if (mb * 8 + g < M) a = __ldg(reinterpret_cast<const uint4*>(a_frag + mb * a_mb + (chunk * CHUNK + u) * 32));
+          mma16816(acc[mb], wa[u].x, wb[u].x, wa[u].y, wb[u].y, a.x, a.y);
+          mma16816(acc[mb], wa[u].z, wb[u].z, wa[u].w, wb[u].w, a.z, a.w);
+        }
+      }
+    }
+    // the next tile's first weights fly while this tile is reduced and written
+    const int next = tile + gridDim.x;
+    if (next < n_tiles) {
+      rows_of(next, w0, w1);
+      request(w0, w1, 0);
+    }
+
+    // partial sums -> shared memory (two buffers, so one barrier per tile is enough)
+    float* red = red_base + buf * RED;
+    buf ^= 1;
+#pragma unroll
+    for (int mb = 0; mb < MB; ++mb) {
+      red[(warp * ROWS + g) * (MP + 1) + mb * 8 + 2 * t] = acc[mb][0];
+      red[(warp * ROWS + g) * (MP + 1) + mb * 8 + 2 * t + 1] = acc[mb][1];
+      red[(warp * ROWS + g + 8) * (MP + 1) + mb * 8 + 2 * t] = acc[mb][2];
+      red[(warp * ROWS + g + 8) * (MP + 1) + mb * 8 + 2 * t + 1] = acc[mb][3];
+    }
+    __syncthreads();
+    auto total = [&](int row, int m) {
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) s += red[(w * ROWS + row) * (MP + 1) + m];
+      return s;
+    };
+    const int n0 = tile * TILE_N;
+    if (MODE == SILU) {
+      bf16* out = reinterpret_cast<bf16*>(C);
+      if (tid < 8 * MP) {
+        const int j = tid & 7, m = tid >> 3;
+        if (m < M && n0 + j < N) {
+          const float gt = bfr(total(j, m)), up = bfr(total(j + 8, m));
+          const float s = bfr(gt / (1.f + expf(-gt)));
+          out[(size_t)m * ldc + n0 + j] = __float2bfloat16_rn(s * up);
+        }
+      }
+    } else if (MODE == RESIDUAL) {
+      bf16* x = reinterpret_cast<bf16*>(C);
+      // thread -> (row = tid % 16, m = tid / 16): a half-warp covers the 16 columns of one batch row
+      if (tid < ROWS * MP) {
+        const int row = tid & 15, m = tid >> 4;
+        const int n = n0 + row;
+        float sq = 0.f;
+        if (m < M && n < N) {
+          const float v = bfr(__bfloat162float(x[(size_t)m * ldc + n]) + bfr(total(row, m)));
+          x[(size_t)m * ldc + n] = __float2bfloat16_rn(v);
+          sq = v * v;
+        }
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
+        if (ss_out && row == 0 && m < M) ss_out[(size_t)tile * SS_STRIDE + m] = sq;
+      }
+    } else {
+      if (tid < ROWS * MP) {
+        const int row = tid & 15, m = tid >> 4;
+        const int n = n0 + row;
+        if (m < M && n < N) {
+          const float s = total(row, m);
+          if (MODE == STORE_F32) reinterpret_cast<float*>(C)[(size_t)m * ldc + n] = s;
+          else reinterpret_cast<bf16*>(C)[(size_t)m * ldc + n] = __float2bfloat16_rn(s);
+        }
+      }
+    }
+  }
+}
+
+template <int MB, int MODE, bool NORM>
+int launch3(const void* A, int lda, const void* W, void* C, int ldc, int M, int N, const float* norm_w,
+            const float* ss_in, int ss_parts, float eps, float* ss_out, int pdl, cudaStream_t st) {
+  constexpr int MP = 8 * MB;
+  size_t smem = (size_t)2 * WARPS * ROWS * (MP + 1) * 4 + SS_STRIDE * 4;
+  if (NORM) smem += (size_t)MP * KA * 2;
+  if (smem > 110 * 1024) return DRYFT_ERR_UNSUPPORTED;
+  static size_t attr_bytes = 48 * 1024;  // per instantiation; raised by an eager launch before any capture
+  if (smem > attr_bytes) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_decode_kernel<MB, MODE, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    attr_bytes = smem;
+  }
+  // persistent blocks: two per SM at most, each taking every grid-th tile; the grid is chosen so
+  // that the tiles divide as evenly as they can
+  static int max_blocks = 0;
+  if (max_blocks == 0) {
+    int dev = 0, sms = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    max_blocks = 2 * (sms > 0 ? sms : 148);
+  }
+  const int n_tiles = MODE == SILU ? (N + 7) / 8 : (N + ROWS - 1) / ROWS;
+  const int rounds = (n_tiles + max_blocks - 1) / max_blocks;
+  const unsigned blocks = (unsigned)((n_tiles + rounds - 1) / rounds);
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(blocks);
+  cfg.blockDim = dim3(THREADS);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_decode_kernel<MB, MODE, NORM>, (const bf16*)A, lda, (const bf16*)W, C, ldc, M,
+                                     N, norm_w, ss_in, ss_parts, eps, ss_out);
+  if (e != cudaSuccess) return (int)e;
+  return launch_status();
+}
+template <int MB, int MODE>
+int launch2(bool norm, const void* A, int lda, const void* W, void* C, int ldc, int M, int N, const float* norm_w,
+            const float* ss_in, int ss_parts, float eps, float* ss_out, int pdl, cudaStream_t st) {
+  return norm ? launch3<MB, MODE, true>(A, lda, W, C, ldc, M, N, norm_w, ss_in, ss_parts, eps, ss_out, pdl, st)
+              : launch3<MB, MODE, false>(A, lda, W, C, ldc, M, N, norm_w, ss_in, ss_parts, eps, ss_out, pdl, st);
+}
+template <int MB>
+int launch1(int mode, bool norm, const void* A, int lda, const void* W, void* C, int ldc, int M, int N,
+            const float* norm_w, const float* ss_in, int ss_parts, float eps, float* ss_out, int pdl, cudaStream_t st) {
+  switch (mode) {
+    case STORE_BF16: return launch2<MB, STORE_BF16>(norm, A, lda, W, C, ldc, M, N, norm_w, ss_in, ss_parts, eps, ss_out, pdl, st);
+    case STORE_F32: return launch2<MB, STORE_F32>(norm, A, lda, W, C, ldc, M, N, norm_w, ss_in, ss_parts, eps, ss_out, pdl, st);
+    case RESIDUAL: return launch2<MB, RESIDUAL>(norm, A, lda, W, C, ldc, M, N, norm_w, ss_in, ss_parts, eps, ss_out, pdl, st);
+    case SILU: return launch2<MB, SILU>(norm, A, lda, W, C, ldc, M, N, norm_w, ss_in, ss_parts, eps, ss_out, pdl, st);
+  }
+  return DRYFT_ERR_UNSUPPORTED;
+}
+}  // namespace
+
+DRYFT_API int dryft_gemm_decode_k() { return K; }
+
+// Same contract as dryft_gemm_small_m (csrc/gemm_small_m.cu) for this library's K.  A residual product
+// of N outputs leaves ceil(N/16) blocks of sums of squares in ss_out.
+DRYFT_API int dryft_gemm_decode(const void* A, int lda, const void* W, void* C, int ldc, int mode, int M, int N,
+                                const float* norm_w, const float* ss_in, int ss_parts, float eps, float* ss_out, int pdl,
+                                cudaStream_t st) {
+  if (M <= 0 || N <= 0) return 0;
+  if ((lda & 7) || M > 16) return DRYFT_ERR_UNSUPPORTED;
+  if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return DRYFT_ERR_UNSUPPORTED;
+  const bool norm = norm_w != nullptr;
+  if (norm && (!ss_in || ss_parts <= 0 || ((uintptr_t)norm_w & 15))) return DRYFT_ERR_UNSUPPORTED;
+  if (M <= 8) return launch1<1>(mode, norm, A, lda, W, C, ldc, M, N, norm_w, ss_in, ss_parts, eps, ss_out, pdl, st);
+  return launch1<2>(mode, norm, A, lda, W, C, ldc, M, N, norm_w, ss_in, ss_parts, eps, ss_out, pdl, st);
+}

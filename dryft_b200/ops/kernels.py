@@ -94,6 +94,23 @@ def attention_rows_lib(head_dim: int, group: int, page: int) -> ctypes.CDLL:
         return lib
 
 
+def gemm_decode_lib(k: int) -> ctypes.CDLL:
+    """The decode matrix product compiled for one inner size ``k`` (a multiple of 256)."""
+    if k <= 0 or k % 256:
+        raise KernelError(f"the specialised decode product takes inner sizes that are multiples of 256, got {k}")
+    key = ("gemm_decode", k)
+    with _lock:
+        lib = _variants.get(key)
+        if lib is None:
+            lib = _load(build.build_library("gemm_decode", ("gemm_decode.cu",), {"DRYFT_K": k}))
+            lib.dryft_gemm_decode.argtypes = [_p, _i, _p, _p, _i, _i, _i, _i, _p, _p, _i, _f, _p, _i, _p]
+            lib.dryft_gemm_decode.restype = _i
+            if lib.dryft_gemm_decode_k() != k:
+                raise KernelError("the compiled decode product is for another inner size")
+            _variants[key] = lib
+        return lib
+
+
 def attention_decode_supported(head_dim: int, group: int) -> bool:
     """Whether the one-launch decode attention exists for these sizes (the query heads of a kv head
     form one 16-row tensor-core operand)."""
@@ -475,6 +492,12 @@ def gemm_small_m(a, w, out, *, mode: str = "store", norm_w=None, ss_in=None, ss_
         _need(ss_in, "ss_in", torch.float32)
         if ss_parts <= 0 or ss_in.numel() < ss_parts * SS_STRIDE:
             raise KernelError("gemm_small_m: ss_in does not hold ss_parts blocks")
+    if k % 256 == 0:  # the form compiled for this inner size: loops unrolled, offsets immediate
+        rc = gemm_decode_lib(k).dryft_gemm_decode(_ptr(a), k, _ptr(w), _ptr(out), n, code, m, n, _ptr(norm_w), _ptr(ss_in),
+                                                  int(ss_parts), float(eps), _ptr(ss_out), int(pdl), _stream())
+        if rc != UNSUPPORTED:  # it refuses what does not fit its shared memory; the general form takes that
+            _ok(rc, f"gemm_decode (M={m}, N={n}, K={k}, mode={mode})")
+            return
     _ok(core().dryft_gemm_small_m(_ptr(a), k, _ptr(w), _ptr(out), n, code, m, n, k, _ptr(norm_w), _ptr(ss_in),
                                   int(ss_parts), float(eps), _ptr(ss_out), int(pdl), _stream()),
         f"gemm_small_m (M={m}, N={n}, K={k}, mode={mode})")

@@ -134,7 +134,7 @@ def test_gemm_f32(m, n, k_):
 
 
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
-@pytest.mark.parametrize("n,k_", [(2560, 2560), (331, 96), (19, 4096), (6144, 1008), (48, 16), (160, 9728)])
+@pytest.mark.parametrize("n,k_", [(2560, 2560), (331, 96), (19, 4096), (6144, 1008), (48, 16), (160, 9728), (100, 256), (333, 1024)])
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_gemm_small_m(m, n, k_, out_dtype):
     k = K()
@@ -152,7 +152,7 @@ def test_gemm_small_m(m, n, k_, out_dtype):
 
 
 @pytest.mark.parametrize("m", [1, 8, 13])
-@pytest.mark.parametrize("n,k_", [(2560, 2560), (96, 176), (200, 1008)])
+@pytest.mark.parametrize("n,k_", [(2560, 2560), (96, 176), (200, 1008), (4096, 1024), (208, 256)])
 def test_gemm_small_m_fused_norm_residual_silu(m, n, k_):
     """The fused forms of the decode product against the plain parts: RMSNorm of the input from
     sums of squares left by an earlier product, residual add with new sums of squares, SiLU*mul."""
