@@ -13,6 +13,7 @@
 //
 // No block waits on another block; there is no spin anywhere in this file.
 #include "common.cuh"
+#include "attn_rows_static.h"
 #include <math.h>
 
 #if !defined(DRYFT_HEAD_DIM) || !defined(DRYFT_GROUP) || !defined(DRYFT_PAGE)
@@ -255,3 +256,48 @@ DRYFT_API int dryft_attn_rows(int is_bf16, const void* q, const void* k_pages, c
                  : launch<float>(q, k_pages, v_pages, page_table, max_pages, tok_slot, tok_pos, out, part_o, part_ml,
                                  n_rows, nKV, n_splits, scale, window, st);
 }
+
+// ------------------------------------------------------------------------------------------
+// The same attention for callers that cannot allocate device memory (see attn_rows_static.h).
+// The split partials live in a file-scope device array instead of buffers handed in.  In host
+// code the array's name is only a stand-in for the symbol, not a device address, so the address
+// is asked of the runtime once per device, with that device current, and kept.
+// ------------------------------------------------------------------------------------------
+namespace {
+static __device__ __align__(256) float g_static_scratch[DRYFT_ATTN_ROWS_STATIC_FLOATS];
+constexpr int MAX_DEVICES = 64;
+float* g_static_scratch_ptr[MAX_DEVICES] = {nullptr};
+}  // namespace
+
+DRYFT_API int dryft_attn_rows_static_scratch(int is_bf16, const void* q, const void* k_pages, const void* v_pages,
+                                             const int* page_table, int max_pages, const int* tok_slot, const int* tok_pos,
+                                             void* out, int n_rows, int nKV, int n_splits, float scale, int window,
+                                             cudaStream_t st) {
+  if (n_rows <= 0) return 0;
+  if (n_splits < 1 || nKV < 1) return DRYFT_ERR_UNSUPPORTED;
+  // partial outputs [rows, heads, splits, D] and (max, sum) pairs [rows, heads, splits, 2]
+  const unsigned long long heads = (unsigned long long)nKV * G;
+  const unsigned long long need_o = (unsigned long long)n_rows * heads * n_splits * D;
+  const unsigned long long need_ml = (unsigned long long)n_rows * heads * n_splits * 2;
+  if (n_splits > 1 && need_o + need_ml > (unsigned long long)DRYFT_ATTN_ROWS_STATIC_FLOATS) return DRYFT_ERR_SCRATCH_TOO_SMALL;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= MAX_DEVICES) return DRYFT_ERR_UNSUPPORTED;
+  if (g_static_scratch_ptr[dev] == nullptr) {  // set-up, once per device: the first call on a device
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&ptr, g_static_scratch);
+    if (e != cudaSuccess) return (int)e;
+    g_static_scratch_ptr[dev] = ptr;
+  }
+  float* part_o = g_static_scratch_ptr[dev];
+  float* part_ml = part_o + need_o;
+  // Nothing in the scratch has to start at zero: every split writes its partial of every
+  // (row, head) before the combining kernel reads any of them.
+  return is_bf16 ? launch<__nv_bfloat16>(q, k_pages, v_pages, page_table, max_pages, tok_slot, tok_pos, out, part_o, part_ml,
+                                         n_rows, nKV, n_splits, scale, window, st)
+                 : launch<float>(q, k_pages, v_pages, page_table, max_pages, tok_slot, tok_pos, out, part_o, part_ml,
+                                 n_rows, nKV, n_splits, scale, window, st);
+}
+
+DRYFT_API long long dryft_attn_rows_static_scratch_floats() { return (long long)DRYFT_ATTN_ROWS_STATIC_FLOATS; }
