@@ -114,31 +114,73 @@ DRYFT_API int dryft_embed(int is_bf16, const int* tokens, const void* table, voi
 //   h[r] = T( w * T( s * rsqrt(mean(s^2) + eps) ) )   weight applied after the cast   (model.py:28-32)
 // The summed row lives in shared memory (hidden floats), so x and delta are read once.
 // ------------------------------------------------------------------------------------------
+// 16-byte vector of T <-> floats
+template <typename T> struct Vec16 { static constexpr int N = 16 / sizeof(T); };
+template <typename T> __device__ __forceinline__ void load_vec(const T* p, float* v) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < Vec16<T>::N; ++i) v[i] = to_f32<T>(e[i]);
+}
+template <typename T> __device__ __forceinline__ void store_vec(T* p, const float* v) {
+  uint4 raw;
+  T* e = reinterpret_cast<T*>(&raw);
+#pragma unroll
+  for (int i = 0; i < Vec16<T>::N; ++i) e[i] = from_f32<T>(v[i]);
+  *reinterpret_cast<uint4*>(p) = raw;
+}
+
 template <typename T>
 __global__ void rmsnorm_kernel(const T* x, const T* __restrict__ delta, const float* __restrict__ w,
                                const int* __restrict__ rows, T* x_out, T* __restrict__ h, int hidden, float eps) {
   // x and x_out may be the same buffer (in-place residual update): no __restrict__ on them
-  extern __shared__ float row[];  // hidden floats + 33 scratch
-  float* scratch = row + hidden;
+  extern __shared__ __align__(16) float row[];  // hidden floats + 33 scratch
+  float* scratch = row + ((hidden + 3) & ~3);
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   const T* xr = x + (size_t)src * hidden;
   const T* dr = delta ? delta + (size_t)src * hidden : nullptr;
+  T* xo = x_out ? x_out + (size_t)src * hidden : nullptr;
+  T* hr = h + (size_t)r * hidden;
+  constexpr int V = Vec16<T>::N;
+  const bool vec = hidden % V == 0;  // rows are then 16-byte aligned too (allocations are)
   float ss = 0.f;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    float v = to_f32<T>(xr[i]);
-    if (dr) v = rnd<T>(v + to_f32<T>(dr[i]));
-    row[i] = v;
-    ss += v * v;
+  if (vec) {
+    for (int i = threadIdx.x * V; i < hidden; i += blockDim.x * V) {
+      float v[V], d[V];
+      load_vec<T>(xr + i, v);
+      if (dr) {
+        load_vec<T>(dr + i, d);
+#pragma unroll
+        for (int e = 0; e < V; ++e) v[e] = rnd<T>(v[e] + d[e]);
+      }
+#pragma unroll
+      for (int e = 0; e < V; ++e) { row[i + e] = v[e]; ss += v[e] * v[e]; }
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      float v = to_f32<T>(xr[i]);
+      if (dr) v = rnd<T>(v + to_f32<T>(dr[i]));
+      row[i] = v;
+      ss += v * v;
+    }
   }
   ss = block_sum(ss, scratch);
   const float inv = rsqrtf(ss / (float)hidden + eps);
-  T* xo = x_out ? x_out + (size_t)src * hidden : nullptr;
-  T* hr = h + (size_t)r * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    float v = row[i];
-    if (xo) xo[i] = from_f32<T>(v);
-    hr[i] = from_f32<T>(w[i] * rnd<T>(v * inv));
+  if (vec) {
+    for (int i = threadIdx.x * V; i < hidden; i += blockDim.x * V) {
+      float v[V], o[V];
+#pragma unroll
+      for (int e = 0; e < V; ++e) { v[e] = row[i + e]; o[e] = w[i + e] * rnd<T>(v[e] * inv); }
+      if (xo) store_vec<T>(xo + i, v);
+      store_vec<T>(hr + i, o);
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      float v = row[i];
+      if (xo) xo[i] = from_f32<T>(v);
+      hr[i] = from_f32<T>(w[i] * rnd<T>(v * inv));
+    }
   }
 }
 
@@ -146,7 +188,7 @@ template <typename T>
 static int rmsnorm_launch(const void* x, const void* delta, const float* w, const int* rows, void* x_out, void* h,
                           int n_rows, int hidden, float eps, cudaStream_t st) {
   if (n_rows <= 0) return 0;
-  size_t smem = (size_t)(hidden + 33) * sizeof(float);
+  size_t smem = (size_t)(((hidden + 3) & ~3) + 33) * sizeof(float);
   if (smem > 200 * 1024) return DRYFT_ERR_UNSUPPORTED;
   static size_t attr_bytes = 48 * 1024;  // per instantiation; raised by an eager launch before any capture
   if (smem > attr_bytes) {
@@ -194,11 +236,36 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ y, int
   float s = rnd<T>(g / (1.f + expf(-g)));
   y[i] = from_f32<T>(s * u);
 }
-DRYFT_API int dryft_silu_mul(int is_bf16, const void* gu, void* y, int rows, int inter, cudaStream_t st) {
-  size_t total = (size_t)rows * inter;
-  if (total == 0) return 0;
-  unsigned blocks = (unsigned)((total + 255) / 256);
-  if (is_bf16) silu_mul_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)y, inter, total);
-  else silu_mul_kernel<float><<<blocks, 256, 0, st>>>((const float*)gu, (float*)y, inter, total);
+// 16 bytes of gate and of up per thread (inter a multiple of the vector width)
+template <typename T>
+__global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ y, int inter, size_t total_vecs) {
+  constexpr int V = Vec16<T>::N;
+  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total_vecs) return;
+  const int vpr = inter / V;
+  size_t r = i / vpr;
+  int c = (int)(i - r * vpr) * V;
+  const T* base = gu + r * (size_t)(2 * inter);
+  float g[V], u[V], o[V];
+  load_vec<T>(base + c, g);
+  load_vec<T>(base + inter + c, u);
+#pragma unroll
+  for (int e = 0; e < V; ++e) o[e] = rnd<T>(g[e] / (1.f + expf(-g[e]))) * u[e];
+  store_vec<T>(y + r * (size_t)inter + c, o);
+}
+template <typename T>
+static int silu_launch(const void* gu, void* y, int rows, int inter, cudaStream_t st) {
+  constexpr int V = Vec16<T>::N;
+  if (inter % V == 0) {
+    size_t total = (size_t)rows * (inter / V);
+    silu_mul_vec_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const T*)gu, (T*)y, inter, total);
+  } else {
+    size_t total = (size_t)rows * inter;
+    silu_mul_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const T*)gu, (T*)y, inter, total);
+  }
   return launch_status();
+}
+DRYFT_API int dryft_silu_mul(int is_bf16, const void* gu, void* y, int rows, int inter, cudaStream_t st) {
+  if ((size_t)rows * inter == 0) return 0;
+  return is_bf16 ? silu_launch<__nv_bfloat16>(gu, y, rows, inter, st) : silu_launch<float>(gu, y, rows, inter, st);
 }

@@ -1,6 +1,6 @@
 // Fused per-head q/k RMSNorm + rotate-half RoPE + write of K and V into the paged cache.
 //
-// One warp per (token, head).  Heads [0, nH) are query heads (norm, rotate, write to q_out);
+// One block per token, a warp per head in turn.  Heads [0, nH) are query heads (norm, rotate, write to q_out);
 // heads [nH, nH+nKV) are key heads (norm, rotate, write into the cache page of the token's
 // position); heads [nH+nKV, nH+2nKV) are value heads (copied into the cache unchanged).
 // Prefill and decode are the same launch: every token carries its own (slot, position).
@@ -16,8 +16,31 @@
 // norm.  R = 0 disables the rotation; has_norm = 0 disables the norm.
 #include "common.cuh"
 
+// two consecutive elements of T <-> two floats
+template <typename T> __device__ __forceinline__ void load2(const T* p, float& a, float& b);
+template <> __device__ __forceinline__ void load2<float>(const float* p, float& a, float& b) {
+  const float2 v = *reinterpret_cast<const float2*>(p);
+  a = v.x; b = v.y;
+}
+template <> __device__ __forceinline__ void load2<__nv_bfloat16>(const __nv_bfloat16* p, float& a, float& b) {
+  const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(p);
+  a = __bfloat162float(v.x); b = __bfloat162float(v.y);
+}
+template <typename T> __device__ __forceinline__ void store2(T* p, float a, float b);
+template <> __device__ __forceinline__ void store2<float>(float* p, float a, float b) {
+  *reinterpret_cast<float2*>(p) = make_float2(a, b);
+}
+template <> __device__ __forceinline__ void store2<__nv_bfloat16>(__nv_bfloat16* p, float a, float b) {
+  *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
+// One block per token, its warps sharing the token's heads.  PAIRS = rotary pairs (j, j + R/2) a
+// lane holds, two neighbouring j at a time; the head is read once, normalised, rotated and written.
+constexpr int ROPE_WARPS = 4;
+constexpr int MAX_PAIRS2 = 4;  // a lane holds up to 4 x 2 pairs: rotary dims up to 512
+
 template <typename T>
-__global__ void qk_norm_rope_store_kernel(
+__global__ void __launch_bounds__(ROPE_WARPS * 32) qk_norm_rope_store_kernel(
     const T* __restrict__ qkv, int qkv_stride,                 // [N, qkv_stride]; q | k | v column blocks
     const float* __restrict__ wq, const float* __restrict__ wk,  // [D] each (ignored if !has_norm)
     const float* __restrict__ inv_freq,                         // [R/2]
@@ -26,71 +49,139 @@ __global__ void qk_norm_rope_store_kernel(
     T* __restrict__ k_pages, T* __restrict__ v_pages,           // [pages, nKV, page_size, D]
     const int* __restrict__ page_table, int max_pages,
     int n_tokens, int nH, int nKV, int D, int R, int page_size, float eps, int has_norm, int write_kv) {
-  const int warps_per_block = blockDim.x >> 5;
-  const int lane = threadIdx.x & 31;
+  const int n = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads_total = nH + (write_kv ? 2 * nKV : 0);
-  const long long item = (long long)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
-  if (item >= (long long)n_tokens * heads_total) return;
-  const int n = (int)(item / heads_total);
-  const int head = (int)(item % heads_total);
   const int slot = tok_slot[n];
   const int pos = tok_pos[n];
-  const T* src = qkv + (size_t)n * qkv_stride + (size_t)head * D;  // q heads, then k heads, then v heads
-
-  T* dst;
-  if (head < nH) {
-    dst = q_out + ((size_t)n * nH + head) * D;
-    if (slot < 0) {  // padding token: a defined (zero) query
-      for (int i = lane; i < D; i += 32) dst[i] = from_f32<T>(0.f);
-      return;
-    }
-  } else {
-    if (slot < 0) return;  // padding token: nothing is cached
-    const int kvh = (head - nH) % nKV;
-    const int page = page_table[(size_t)slot * max_pages + pos / page_size];
-    const size_t off = (((size_t)page * nKV + kvh) * page_size + (pos % page_size)) * D;
-    if (head >= nH + nKV) {  // value head: plain copy
-      T* vd = v_pages + off;
-      for (int i = lane; i < D; i += 32) vd[i] = src[i];
-      return;
-    }
-    dst = k_pages + off;
-  }
-
-  float inv = 1.f;
-  const float* w = head < nH ? wq : wk;
-  if (has_norm) {
-    float ss = 0.f;
-    for (int i = lane; i < D; i += 32) {
-      float v = to_f32<T>(src[i]);
-      ss += v * v;
-    }
-    ss = warp_sum(ss);
-    inv = rsqrtf(ss / (float)D + eps);
-  }
   const int half = R >> 1;
-  for (int j = lane; j < half; j += 32) {
-    float a = to_f32<T>(src[j]);
-    float b = to_f32<T>(src[j + half]);
-    if (has_norm) {
-      a = rnd<T>(rnd<T>(a * inv) * w[j]);
-      b = rnd<T>(rnd<T>(b * inv) * w[j + half]);
+  size_t page_off = 0;
+  if (slot >= 0 && write_kv)
+    page_off = ((size_t)page_table[(size_t)slot * max_pages + pos / page_size] * nKV * page_size + (pos % page_size)) * D;
+
+  // the token's angles: cos/sin of pos * inv_freq[j] for this lane's pairs (the same for every head)
+  float cs[MAX_PAIRS2][2], sn[MAX_PAIRS2][2];
+#pragma unroll
+  for (int i = 0; i < MAX_PAIRS2; ++i) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int j = 2 * lane + 64 * i + e;
+      cs[i][e] = 1.f;
+      sn[i][e] = 0.f;
+      if (j < half) {
+        float s_, c_;
+        sincosf((float)pos * inv_freq[j], &s_, &c_);
+        cs[i][e] = rnd<T>(c_);
+        sn[i][e] = rnd<T>(s_);
+      }
     }
-    float ang = (float)pos * inv_freq[j];
-    float sn, cs;
-    sincosf(ang, &sn, &cs);
-    cs = rnd<T>(cs);
-    sn = rnd<T>(sn);
-    // separate roundings of the two products, then of the sum (no fused multiply-add across them)
-    float o1 = __fadd_rn(rnd<T>(__fmul_rn(a, cs)), -rnd<T>(__fmul_rn(b, sn)));
-    float o2 = __fadd_rn(rnd<T>(__fmul_rn(b, cs)), rnd<T>(__fmul_rn(a, sn)));
-    dst[j] = from_f32<T>(o1);
-    dst[j + half] = from_f32<T>(o2);
   }
-  for (int i = R + lane; i < D; i += 32) {  // dims beyond the rotary part
-    float a = to_f32<T>(src[i]);
-    if (has_norm) a = rnd<T>(rnd<T>(a * inv) * w[i]);
-    dst[i] = from_f32<T>(a);
+
+  for (int head = warp; head < heads_total; head += ROPE_WARPS) {
+    const T* src = qkv + (size_t)n * qkv_stride + (size_t)head * D;  // q heads, then k heads, then v heads
+    T* dst;
+    if (head < nH) {
+      dst = q_out + ((size_t)n * nH + head) * D;
+      if (slot < 0) {  // padding token: a defined (zero) query
+        for (int i = lane; i < D; i += 32) dst[i] = from_f32<T>(0.f);
+        continue;
+      }
+    } else {
+      if (slot < 0) continue;  // padding token: nothing is cached
+      const int kvh = (head - nH) % nKV;
+      const size_t off = page_off + (size_t)kvh * page_size * D;
+      if (head >= nH + nKV) {  // value head: plain copy
+        T* vd = v_pages + off;
+        if ((D & 1) == 0) {
+          for (int i = 2 * lane; i < D; i += 64) { float a, b; load2<T>(src + i, a, b); store2<T>(vd + i, a, b); }
+        } else {
+          for (int i = lane; i < D; i += 32) vd[i] = src[i];
+        }
+        continue;
+      }
+      dst = k_pages + off;
+    }
+    const float* w = head < nH ? wq : wk;
+    if ((half & 1) == 0 && half <= 64 * MAX_PAIRS2) {
+      // vector path: the lane's pairs live in registers; one read of the head
+      float a[MAX_PAIRS2][2], b[MAX_PAIRS2][2];
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < MAX_PAIRS2; ++i) {
+        const int j = 2 * lane + 64 * i;
+        a[i][0] = a[i][1] = b[i][0] = b[i][1] = 0.f;
+        if (j < half) {
+          load2<T>(src + j, a[i][0], a[i][1]);
+          load2<T>(src + j + half, b[i][0], b[i][1]);
+          ss += a[i][0] * a[i][0] + a[i][1] * a[i][1] + b[i][0] * b[i][0] + b[i][1] * b[i][1];
+        }
+      }
+      float inv = 1.f;
+      if (has_norm) {
+        for (int i = R + lane; i < D; i += 32) {  // dims beyond the rotary part count too
+          const float v = to_f32<T>(src[i]);
+          ss += v * v;
+        }
+        ss = warp_sum(ss);
+        inv = rsqrtf(ss / (float)D + eps);
+      }
+#pragma unroll
+      for (int i = 0; i < MAX_PAIRS2; ++i) {
+        const int j = 2 * lane + 64 * i;
+        if (j < half) {
+          float o1[2], o2[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            float x = a[i][e], y = b[i][e];
+            if (has_norm) {
+              x = rnd<T>(rnd<T>(x * inv) * w[j + e]);
+              y = rnd<T>(rnd<T>(y * inv) * w[j + e + half]);
+            }
+            // separate roundings of the two products, then of the sum (no fused multiply-add across them)
+            o1[e] = __fadd_rn(rnd<T>(__fmul_rn(x, cs[i][e])), -rnd<T>(__fmul_rn(y, sn[i][e])));
+            o2[e] = __fadd_rn(rnd<T>(__fmul_rn(y, cs[i][e])), rnd<T>(__fmul_rn(x, sn[i][e])));
+          }
+          store2<T>(dst + j, o1[0], o1[1]);
+          store2<T>(dst + j + half, o2[0], o2[1]);
+        }
+      }
+      for (int i = R + lane; i < D; i += 32) {  // dims beyond the rotary part
+        float x = to_f32<T>(src[i]);
+        if (has_norm) x = rnd<T>(rnd<T>(x * inv) * w[i]);
+        dst[i] = from_f32<T>(x);
+      }
+    } else {
+      // general path: any even rotary size, element by element
+      float inv = 1.f;
+      if (has_norm) {
+        float ss = 0.f;
+        for (int i = lane; i < D; i += 32) {
+          const float v = to_f32<T>(src[i]);
+          ss += v * v;
+        }
+        ss = warp_sum(ss);
+        inv = rsqrtf(ss / (float)D + eps);
+      }
+      for (int j = lane; j < half; j += 32) {
+        float x = to_f32<T>(src[j]);
+        float y = to_f32<T>(src[j + half]);
+        if (has_norm) {
+          x = rnd<T>(rnd<T>(x * inv) * w[j]);
+          y = rnd<T>(rnd<T>(y * inv) * w[j + half]);
+        }
+        float s_, c_;
+        sincosf((float)pos * inv_freq[j], &s_, &c_);
+        c_ = rnd<T>(c_);
+        s_ = rnd<T>(s_);
+        dst[j] = from_f32<T>(__fadd_rn(rnd<T>(__fmul_rn(x, c_)), -rnd<T>(__fmul_rn(y, s_))));
+        dst[j + half] = from_f32<T>(__fadd_rn(rnd<T>(__fmul_rn(y, c_)), rnd<T>(__fmul_rn(x, s_))));
+      }
+      for (int i = R + lane; i < D; i += 32) {
+        float x = to_f32<T>(src[i]);
+        if (has_norm) x = rnd<T>(rnd<T>(x * inv) * w[i]);
+        dst[i] = from_f32<T>(x);
+      }
+    }
   }
 }
 
@@ -101,12 +192,7 @@ static int launch(const void* qkv, int qkv_stride, const float* wq, const float*
                   float eps, int has_norm, int write_kv, cudaStream_t st) {
   if (n_tokens <= 0) return 0;
   if (D <= 0 || (R & 1) || R > D || R < 0) return DRYFT_ERR_UNSUPPORTED;
-  const int heads_total = nH + (write_kv ? 2 * nKV : 0);
-  const long long items = (long long)n_tokens * heads_total;
-  const int warps = 8;
-  const long long blocks = (items + warps - 1) / warps;
-  if (blocks > 0x7fffffffLL) return DRYFT_ERR_UNSUPPORTED;
-  qk_norm_rope_store_kernel<T><<<(unsigned)blocks, warps * 32, 0, st>>>(
+  qk_norm_rope_store_kernel<T><<<(unsigned)n_tokens, ROPE_WARPS * 32, 0, st>>>(
       (const T*)qkv, qkv_stride, wq, wk, inv_freq, tok_slot, tok_pos, (T*)q_out, (T*)k_pages, (T*)v_pages, page_table,
       max_pages, n_tokens, nH, nKV, D, R, page_size, eps, has_norm, write_kv);
   return launch_status();
