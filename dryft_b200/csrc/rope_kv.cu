@@ -1,6 +1,6 @@
 // Fused per-head q/k RMSNorm + rotate-half RoPE + write of K and V into the paged cache.
 //
-// One block per token, a warp per head in turn.  Heads [0, nH) are query heads (norm, rotate, write to q_out);
+// One warp per (token, head).  Heads [0, nH) are query heads (norm, rotate, write to q_out);
 // heads [nH, nH+nKV) are key heads (norm, rotate, write into the cache page of the token's
 // position); heads [nH+nKV, nH+2nKV) are value heads (copied into the cache unchanged).
 // Prefill and decode are the same launch: every token carries its own (slot, position).
@@ -34,8 +34,8 @@ template <> __device__ __forceinline__ void store2<__nv_bfloat16>(__nv_bfloat16*
   *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
 }
 
-// One block per token, its warps sharing the token's heads.  PAIRS = rotary pairs (j, j + R/2) a
-// lane holds, two neighbouring j at a time; the head is read once, normalised, rotated and written.
+// A lane holds rotary pairs (j, j + R/2), two neighbouring j at a time; the head is read once,
+// normalised, rotated and written.
 constexpr int ROPE_WARPS = 4;
 constexpr int MAX_PAIRS2 = 4;  // a lane holds up to 4 x 2 pairs: rotary dims up to 512
 
@@ -49,9 +49,13 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) qk_norm_rope_store_kernel(
     T* __restrict__ k_pages, T* __restrict__ v_pages,           // [pages, nKV, page_size, D]
     const int* __restrict__ page_table, int max_pages,
     int n_tokens, int nH, int nKV, int D, int R, int page_size, float eps, int has_norm, int write_kv) {
-  const int n = blockIdx.x;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // a warp per (token, head): plenty of warps in flight hide the latency of the few loads each one has
+  const int lane = threadIdx.x & 31;
   const int heads_total = nH + (write_kv ? 2 * nKV : 0);
+  const long long item = (long long)blockIdx.x * ROPE_WARPS + (threadIdx.x >> 5);
+  if (item >= (long long)n_tokens * heads_total) return;
+  const int n = (int)(item / heads_total);
+  const int head0 = (int)(item - (long long)n * heads_total);
   const int slot = tok_slot[n];
   const int pos = tok_pos[n];
   const int half = R >> 1;
@@ -59,7 +63,7 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) qk_norm_rope_store_kernel(
   if (slot >= 0 && write_kv)
     page_off = ((size_t)page_table[(size_t)slot * max_pages + pos / page_size] * nKV * page_size + (pos % page_size)) * D;
 
-  // the token's angles: cos/sin of pos * inv_freq[j] for this lane's pairs (the same for every head)
+  // the token's angles: cos/sin of pos * inv_freq[j] for this lane's pairs
   float cs[MAX_PAIRS2][2], sn[MAX_PAIRS2][2];
 #pragma unroll
   for (int i = 0; i < MAX_PAIRS2; ++i) {
@@ -68,7 +72,7 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) qk_norm_rope_store_kernel(
       const int j = 2 * lane + 64 * i + e;
       cs[i][e] = 1.f;
       sn[i][e] = 0.f;
-      if (j < half) {
+      if (j < half && head0 < nH + nKV && slot >= 0) {  // value heads and padding tokens rotate nothing
         float s_, c_;
         sincosf((float)pos * inv_freq[j], &s_, &c_);
         cs[i][e] = rnd<T>(c_);
@@ -77,7 +81,7 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) qk_norm_rope_store_kernel(
     }
   }
 
-  for (int head = warp; head < heads_total; head += ROPE_WARPS) {
+  for (int head = head0; head == head0; ++head) {
     const T* src = qkv + (size_t)n * qkv_stride + (size_t)head * D;  // q heads, then k heads, then v heads
     T* dst;
     if (head < nH) {
@@ -192,7 +196,10 @@ static int launch(const void* qkv, int qkv_stride, const float* wq, const float*
                   float eps, int has_norm, int write_kv, cudaStream_t st) {
   if (n_tokens <= 0) return 0;
   if (D <= 0 || (R & 1) || R > D || R < 0) return DRYFT_ERR_UNSUPPORTED;
-  qk_norm_rope_store_kernel<T><<<(unsigned)n_tokens, ROPE_WARPS * 32, 0, st>>>(
+  const long long items = (long long)n_tokens * (nH + (write_kv ? 2 * nKV : 0));
+  const long long blocks = (items + ROPE_WARPS - 1) / ROPE_WARPS;
+  if (blocks > 0x7fffffffLL) return DRYFT_ERR_UNSUPPORTED;
+  qk_norm_rope_store_kernel<T><<<(unsigned)blocks, ROPE_WARPS * 32, 0, st>>>(
       (const T*)qkv, qkv_stride, wq, wk, inv_freq, tok_slot, tok_pos, (T*)q_out, (T*)k_pages, (T*)v_pages, page_table,
       max_pages, n_tokens, nH, nKV, D, R, page_size, eps, has_norm, write_kv);
   return launch_status();
