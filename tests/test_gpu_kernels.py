@@ -199,6 +199,40 @@ def test_gemm_small_m_fused_norm_residual_silu(m, n, k_):
     torch.testing.assert_close(act.cpu().float(), want.float(), rtol=3e-2, atol=3e-2)
 
 
+@pytest.mark.parametrize("m,n,k_", [(128, 256, 64), (100, 300, 128), (333, 2560, 512), (2048, 1024, 2560)])
+@pytest.mark.parametrize("mode", ["store", "residual", "silu"])
+def test_gemm_tc(m, n, k_, mode):
+    """The tcgen05 / TMEM / TMA product (prefill) against a 64-bit reference: plain store, residual add
+    in place, SiLU*mul over gate rows then up rows; row and column counts that are no multiple of the
+    128 x 256 tile."""
+    k = K()
+    bf = torch.bfloat16
+    a = torch.randn(m, k_, device=DEV).to(bf)
+    rows = 2 * n if mode == "silu" else n
+    w = (torch.randn(rows, k_, device=DEV) / math.sqrt(k_)).to(bf)
+    out = torch.randn(m, n, device=DEV).to(bf)
+    x0 = out.clone()
+    k.gemm_tc(a, w, out, mode=mode)
+    torch.cuda.synchronize()
+    k.check_error_flags()
+    prod = P.matmul_nt(a.cpu(), w.cpu(), bf)
+    if mode == "store":
+        want = prod
+    elif mode == "residual":
+        want = P.residual_add(x0.cpu(), prod)
+    else:
+        want = P.silu_mul(prod[:, :n], prod[:, n:])
+    torch.testing.assert_close(out.cpu().float(), want.float(), rtol=2e-2, atol=3e-2)
+
+
+def test_gemm_tc_refuses_what_it_cannot_take():
+    k = K()
+    a = torch.zeros(128, 96, device=DEV, dtype=torch.bfloat16)  # K is no multiple of 64
+    w = torch.zeros(64, 96, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(k.KernelError):
+        k.gemm_tc(a, w, torch.empty(128, 64, device=DEV, dtype=torch.bfloat16))
+
+
 def test_gemm_small_m_refuses_odd_k():
     k = K()
     a = torch.zeros(2, 12, device=DEV, dtype=torch.bfloat16)
