@@ -48,6 +48,7 @@ class EngineOptions:
     small_m_max: int = 16
     fuse_decode: bool = True               # fold norms, adds and SiLU*mul into the decode products
     pdl: bool = True                       # programmatic dependent launch between the decode products
+    tcgen05: bool = True                   # prefill attention on tcgen05 / TMEM / TMA where the head size allows
 
 
 def _require_cuda(device: str) -> torch.device:
@@ -96,7 +97,7 @@ class Engine:
         self.dtype = dtype
         props = torch.cuda.get_device_properties(dev)
         self.rt = Runtime(dtype=dtype, device=dev, page_size=opts.page_size, sm_count=props.multi_processor_count,
-                          small_m_max=opts.small_m_max, fuse_decode=opts.fuse_decode, pdl=opts.pdl)
+                          small_m_max=opts.small_m_max, fuse_decode=opts.fuse_decode, pdl=opts.pdl, tcgen05=opts.tcgen05)
         with torch.cuda.device(dev), torch.no_grad():
             self.model = DecoderModel(spec, source, self.rt)
             self.max_seq_len = opts.max_seq_len or min(spec.max_positions, 8192)
@@ -161,6 +162,9 @@ class _DeviceBackend:
 
     def close(self, handles: Sequence[int]) -> None:
         self.e.cache.close_sequences(handles)
+        from ..ops import kernels as K
+
+        K.check_error_flags()  # a kernel that gave up a bounded wait makes the batch's results invalid
 
     def _ints(self, vals: Sequence[int]) -> torch.Tensor:
         return torch.tensor(list(vals), dtype=torch.int32).to(self.e.device, non_blocking=True)

@@ -22,7 +22,6 @@ import torch
 
 from ..cache.store import SequenceCache
 from ..ops import kernels as K
-from ..parts.attention import PREFILL_TILE
 from ..parts.base import Runtime, StepContext
 from .model import DecoderModel
 
@@ -36,6 +35,8 @@ class Stepper:
         self._graphs: Dict[tuple, "_DecodeGraph"] = {}
         self._pinned: Optional[torch.Tensor] = None
         self._upload_event: Optional[torch.cuda.Event] = None
+        # query tokens per prefill tile: the smallest any mixer asks for (64 unless every mixer takes more)
+        self.prefill_tile = min([getattr(b.mixer, "prefill_tile", 64) for b in model.blocks] or [64])
         self.last_decode_slots: Optional[torch.Tensor] = None
 
     # ------------------------------------------------------------------ host -> device metadata
@@ -81,8 +82,8 @@ class Stepper:
         if not decode:
             order = []
             for b, q in enumerate(q_lens):
-                for q0 in range(0, q, PREFILL_TILE):
-                    order.append((starts[b] + q0, cu[b] + q0, min(PREFILL_TILE, q - q0)))
+                for q0 in range(0, q, self.prefill_tile):
+                    order.append((starts[b] + q0, cu[b] + q0, min(self.prefill_tile, q - q0)))
             order.sort(key=lambda t: -t[0])  # tiles with the most keys first
             tiles0 = [t[1] for t in order]
             tilesn = [t[2] for t in order]
@@ -102,7 +103,7 @@ class Stepper:
         K.step_meta(d_cu, d_slot, self.cache.seq_len, tok_slot, tok_pos, N, B)
         ctx = StepContext(n_tokens=N, n_seqs=B, tokens=d_tokens, cu_q=d_cu, seq_slot=d_slot, tok_slot=tok_slot,
                           tok_pos=tok_pos, decode=decode, max_kv=max(st + q for st, q in zip(starts, q_lens)),
-                          tile_tok0=d_t0 if T else None, tile_rows=d_tn if T else None, n_tiles=T, tile_size=PREFILL_TILE)
+                          tile_tok0=d_t0 if T else None, tile_rows=d_tn if T else None, n_tiles=T, tile_size=self.prefill_tile)
         logits = self.model.forward(ctx, self.cache, d_rows if W else None, W)
         K.step_advance(d_cu, d_slot, self.cache.seq_len, B)
         for s, q in zip(slots, q_lens):

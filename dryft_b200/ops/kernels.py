@@ -168,6 +168,28 @@ def attention_decode_lib(head_dim: int, group: int, page: int) -> ctypes.CDLL:
         return lib
 
 
+def attention_prefill_tc_supported(head_dim: int, group: int, page: int) -> bool:
+    """Whether the tcgen05 prefill attention exists for these sizes."""
+    return head_dim in (64, 128) and page == 64 and group >= 1
+
+
+def attention_prefill_tc_lib(head_dim: int, group: int, page: int) -> ctypes.CDLL:
+    """The tcgen05 / TMEM / TMA prefill attention compiled for these sizes."""
+    if not attention_prefill_tc_supported(head_dim, group, page):
+        raise KernelError(f"tcgen05 prefill attention takes head sizes 64 and 128 and 64-token pages, got {head_dim}, {page}")
+    key = ("prefill_tc", head_dim, group, page)
+    with _lock:
+        lib = _variants.get(key)
+        if lib is None:
+            path = build.build_library("attn_prefill_tc", ("attn_prefill_tc.cu",),
+                                       {"DRYFT_HEAD_DIM": head_dim, "DRYFT_GROUP": group, "DRYFT_PAGE": page})
+            lib = _load(path)
+            lib.dryft_attn_prefill_tc.argtypes = [_p, _p, _p, _p, _i, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i, _f, _i, _p, _p]
+            lib.dryft_attn_prefill_tc.restype = _i
+            _variants[key] = lib
+        return lib
+
+
 _tickets: Dict[int, torch.Tensor] = {}
 
 
@@ -461,6 +483,32 @@ def attn_prefill(q, k_pages, v_pages, page_table, tile_tok0, tile_rows, tok_slot
                                _ptr(tile_tok0), _ptr(tile_rows), _ptr(tok_slot), _ptr(tok_pos), _ptr(out), n_tiles,
                                n_heads, n_kv, float(scale), int(window or 0), _stream()),
         f"attn_prefill (head_dim {head_dim})")
+
+
+def attn_prefill_tc(q, k_pages, v_pages, page_table, tile_tok0, tile_rows, tok_slot, tok_pos, out, n_tiles: int,
+                    scale: float, window: Optional[int]) -> None:
+    """``attn_prefill`` on the 5th-generation tensor cores (tcgen05.mma, tensor memory, TMA); tiles of up
+    to 128 query tokens; head sizes 64 and 128."""
+    n, n_heads, head_dim = q.shape
+    _need(q, "q", torch.bfloat16)
+    n_kv = k_pages.shape[1]
+    page = k_pages.shape[2]
+    _need(k_pages, "k_pages", torch.bfloat16, (None, n_kv, page, head_dim))
+    _need(v_pages, "v_pages", torch.bfloat16, tuple(k_pages.shape))
+    for t, nm in ((page_table, "page_table"), (tile_tok0, "tile_tok0"), (tile_rows, "tile_rows"),
+                  (tok_slot, "tok_slot"), (tok_pos, "tok_pos")):
+        _need(t, nm, torch.int32)
+    if tile_tok0.numel() < n_tiles or tile_rows.numel() < n_tiles:
+        raise KernelError("attn_prefill_tc: tile arrays shorter than the tile count")
+    _need(out, "attention output", torch.bfloat16, (n, n_heads * head_dim))
+    if n_heads % n_kv:
+        raise KernelError(f"attn_prefill_tc: {n_heads} query heads are not a multiple of {n_kv} kv heads")
+    lib = attention_prefill_tc_lib(head_dim, n_heads // n_kv, page)
+    _ok(lib.dryft_attn_prefill_tc(_ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(page_table), page_table.shape[1],
+                                  _ptr(tile_tok0), _ptr(tile_rows), _ptr(tok_slot), _ptr(tok_pos), _ptr(out), n_tiles, n,
+                                  k_pages.shape[0], n_heads, n_kv, float(scale), int(window or 0),
+                                  _ptr(error_flag(q.device)), _stream()),
+        f"attn_prefill_tc (head_dim {head_dim})")
 
 
 # ----------------------------------------------------------------------------- matrix products

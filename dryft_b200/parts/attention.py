@@ -25,7 +25,8 @@ from ..ops import kernels as K
 from .base import NORMS, POSITIONS, Runtime, StepContext, TensorInfo, register_mixer
 from .linear import linear
 
-PREFILL_TILE = 64  # query rows per block of the tensor-core prefill kernel
+PREFILL_TILE = 64      # query rows per block of the mma.sync prefill kernel
+PREFILL_TILE_TC = 128  # query rows per block of the tcgen05 prefill kernel
 
 
 @register_mixer("attention")
@@ -76,6 +77,11 @@ class Attention:
         K.attention_rows_lib(self.head_dim, self.group, rt.page_size)
         self.use_prefill_kernel = rt.is_bf16
         self.use_decode_kernel = rt.is_bf16 and rt.fuse_decode and K.attention_decode_supported(self.head_dim, self.group)
+        # prompts: tcgen05 / TMEM / TMA where the head size allows, else mma.sync
+        self.use_prefill_tc = rt.is_bf16 and rt.tcgen05 and K.attention_prefill_tc_supported(self.head_dim, self.group, rt.page_size)
+        self.prefill_tile = PREFILL_TILE_TC if self.use_prefill_tc else PREFILL_TILE
+        if self.use_prefill_tc:
+            K.attention_prefill_tc_lib(self.head_dim, self.group, rt.page_size)
         if self.use_prefill_kernel:
             K.attention_prefill_lib(self.head_dim, self.group, rt.page_size)
         if self.use_decode_kernel:
@@ -149,7 +155,10 @@ class Attention:
                              cache.k, cache.v, cache.page_table, self.n_heads, self.n_kv, self.head_dim,
                              self.position.rotary_dim, self.qk_eps, write_kv=owns_cache)
         o = torch.empty((n, self.q_dim), dtype=h.dtype, device=dev)
-        if self.use_prefill_kernel and not ctx.decode and ctx.n_tiles > 0:
+        if self.use_prefill_tc and not ctx.decode and ctx.n_tiles > 0 and ctx.tile_size <= PREFILL_TILE_TC:
+            K.attn_prefill_tc(q, cache.k, cache.v, cache.page_table, ctx.tile_tok0, ctx.tile_rows, ctx.tok_slot, ctx.tok_pos,
+                              o, ctx.n_tiles, self.scale, self.window)
+        elif self.use_prefill_kernel and not ctx.decode and ctx.n_tiles > 0 and ctx.tile_size <= PREFILL_TILE:
             K.attn_prefill(q, cache.k, cache.v, cache.page_table, ctx.tile_tok0, ctx.tile_rows, ctx.tok_slot, ctx.tok_pos,
                            o, ctx.n_tiles, self.scale, self.window)
         else:

@@ -53,6 +53,7 @@ class Runtime:
     ffn_chunk_rows: int = 16384  # rows of the feed-forward processed at once (bounds [rows, 2I])
     fuse_decode: bool = True     # few rows: fold norms, residual adds and SiLU*mul into the products
     pdl: bool = True             # launch the fused decode products as programmatic dependents
+    tcgen05: bool = True         # prompts: attention on tcgen05.mma / tensor memory / TMA where sizes allow
 
     @property
     def is_bf16(self) -> bool:

@@ -495,6 +495,45 @@ def test_attn_prefill(n_heads, n_kv, d, window):
     torch.testing.assert_close(out.cpu().float(), ref, rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("n_heads,n_kv,d", [(8, 2, 128), (3, 3, 64), (4, 1, 128)])
+@pytest.mark.parametrize("window", [None, 40])
+def test_attn_prefill_tc(n_heads, n_kv, d, window):
+    """The tcgen05 prefill attention against plain attention: packed prompts of unequal lengths, tiles
+    of up to 128 tokens, some continuing an earlier chunk."""
+    k = K()
+    dtype = torch.bfloat16
+    page, tile = 64, 128
+    scale = 1.0 / math.sqrt(d)
+    plan = [(3, 0, 1), (0, 0, 300), (5, 100, 77), (1, 64, 128), (2, 0, 129)]  # (slot, cached, new)
+    seqs = {}
+    for slot, old, new in plan:
+        L = old + new
+        seqs[slot] = (torch.randn(L, n_kv, d).to(dtype), torch.randn(L, n_kv, d).to(dtype))
+    kc, vc, pt = _fill_cache(seqs, n_kv, d, page, dtype, n_pages=24, max_pages=6, slots=6, scatter_seed=5)
+    tok_slot, tok_pos, tiles0, tilesn, qs, refs = [], [], [], [], [], []
+    base = 0
+    for slot, old, new in plan:
+        q = torch.randn(new, n_heads, d).to(dtype)
+        qs.append(q)
+        for i in range(new):
+            tok_slot.append(slot)
+            tok_pos.append(old + i)
+            refs.append(_attn_ref(q[i], seqs[slot][0], seqs[slot][1], old + i, scale, window))
+        for q0 in range(0, new, tile):
+            tiles0.append(base + q0)
+            tilesn.append(min(tile, new - q0))
+        base += new
+    n = base
+    out = torch.full((n, n_heads * d), 9.0, device=DEV, dtype=dtype)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    k.attn_prefill_tc(torch.cat(qs).to(DEV), kc, vc, pt, i32(tiles0), i32(tilesn), i32(tok_slot), i32(tok_pos), out,
+                      len(tiles0), scale, window)
+    torch.cuda.synchronize()
+    k.check_error_flags()
+    assert torch.isfinite(out.float()).all()
+    torch.testing.assert_close(out.cpu().float(), torch.stack(refs), rtol=2e-2, atol=2e-2)
+
+
 # ------------------------------------------------------------------------------------ token choice
 def test_argmax_rows_ties_and_state():
     k = K()
