@@ -1,19 +1,24 @@
 // Prefill attention on the 5th-generation tensor cores (bfloat16): causal grouped-query attention of
 // packed prompts of unequal lengths over the paged cache, with Q K^T and P V issued as tcgen05.mma,
-// S and the per-tile P V product in tensor memory, and Q, K and V brought in by TMA.  Same operation,
-// same masks and same rounding points as csrc/attn_prefill.cu (which stays as the general form);
-// compiled per model with -DDRYFT_HEAD_DIM (64 or 128), -DDRYFT_GROUP, -DDRYFT_PAGE (64).
+// S, P and O in tensor memory, and Q, K and V brought in by TMA.  Same operation and same masks as
+// csrc/attn_prefill.cu (which stays as the general form); compiled per model with -DDRYFT_HEAD_DIM
+// (64 or 128), -DDRYFT_GROUP, -DDRYFT_PAGE (64).
 //
-// Grid (query tiles, query heads).  A tile is up to 128 consecutive query tokens of ONE sequence.
-//   warp 4, one thread ("driver")  TMA: the Q tile once (3-D map over [token, head, d]), then page after
-//       page of K and V (2-D maps over the page pool, 64 keys x 64 d boxes, 128-byte swizzle) into a
-//       two-stage ring; tcgen05.mma: S = Q K^T (M 128, N 64, K = head size; both operands K-major) into
-//       64 columns of tensor memory, and, once the softmax warps have left P in shared memory,
-//       T = P V (M 128, N = head size, K 64; V is the MN-major operand) into the columns beside them.
-//   warps 0-3, one thread per query row   tcgen05.ld S, scale, mask (key <= query position, window),
-//       running maximum and sum in 32-bit (log2 domain), P rounded to bfloat16 and written to shared
-//       memory in the swizzled K-major layout the MMA reads; then tcgen05.ld T and
-//       O = O * alpha + T in registers.  At the end O / l is rounded and stored.
+// Grid (query tiles, query heads); two blocks share an SM, so that one block's softmax runs under the
+// other's products.  A tile is up to 128 consecutive query tokens of ONE sequence.
+//   warp 4, one thread   TMA: the Q tile once (3-D map over [token, head, d]), then page after page of K
+//       and of V (2-D maps over the page pool, 64 keys x 64 d boxes, 128-byte swizzle) into two rings of
+//       their own: a K stage is free again as soon as its S product is done, a V stage after its P V.
+//   warp 5, one thread   tcgen05.mma: S_j = Q K_j^T (M 128, N 64, K = head size; both operands K-major
+//       in shared memory) into one of two 64-column buffers of tensor memory, one tile ahead of the
+//       softmax; then, once P_j is in tensor memory, O += P_j V_j (M 128, N = head size, K 64; P is the
+//       operand read from tensor memory, V the MN-major operand in shared memory).
+//   warps 0-3, one thread per query row   tcgen05.ld S, mask (key <= query position, window) on the
+//       tiles that need one, running maximum and sum in 32-bit (log2 domain), P rounded to bfloat16 and
+//       stored over the first 32 columns of its own S buffer (two keys a column).  The running maximum
+//       moves only when it grows by more than 8 (a factor of 256 in P, exact in 32-bit and harmless in
+//       bfloat16); only then is O in tensor memory rescaled (tcgen05.ld / st), after the P V product
+//       before it has finished.  At the end O / l is rounded and stored.
 // hari495/dryft uses SDPA's flash kernel here (engine/dryft_qwen3/model.py:172-177).
 //
 // Every mbarrier wait is bounded by a clock (about a second); a waiter that gives up raises *err and
@@ -41,12 +46,17 @@ constexpr int KV_ATOM = BN * 128;   // bytes of one K or V atom [64 keys][64 d]
 constexpr int Q_BYTES = DA * Q_ATOM;
 constexpr int K_BYTES = DA * KV_ATOM;
 constexpr int V_BYTES = DA * KV_ATOM;
-constexpr int P_BYTES = BM * 128;   // [128 rows][64 keys]
-constexpr int KV_STAGES = 2;
-constexpr int SMEM_BYTES = Q_BYTES + KV_STAGES * (K_BYTES + V_BYTES) + P_BYTES + 1024 + 256;
-constexpr int THREADS = 160;
-constexpr int TMEM_COLS = 256;      // S: columns 0..63, T: columns 64..64+D-1
-constexpr int T_COL = 64;
+// Stages of the K ring and of the V ring.  Two blocks of 256 tensor-memory columns fill an SM's 512, and
+// the shared memory asked for keeps a third block off the SM, so that no allocation ever has to wait.
+constexpr int STAGES = D == 128 ? 2 : 4;
+constexpr int N_BARS = 1 + 4 * STAGES + 2 + 2 + 1;
+constexpr int SMEM_BYTES = Q_BYTES + STAGES * (K_BYTES + V_BYTES) + 1024 + 8 * N_BARS + 16;
+static_assert(3 * (SMEM_BYTES + 1024) > 227 * 1024 && 2 * (SMEM_BYTES + 1024) <= 227 * 1024, "two blocks an SM");
+constexpr int THREADS = 192;
+constexpr int TMEM_COLS = 256;      // S buffers at columns 0 and 64 (P over the first 32 of each), O from 128 on
+constexpr int S_COL = 64;           // columns of one S buffer
+constexpr int O_COL = 128;
+constexpr float GROW = 8.f;         // the running maximum moves when it grows by more than this (log2)
 constexpr long long WAIT_CYCLES = 2000000000LL;
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -107,8 +117,13 @@ __device__ __forceinline__ void umma(unsigned d_tmem, unsigned long long a_desc,
 __device__ __forceinline__ void umma_commit(void* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
-__device__ __forceinline__ void tmem_ld32(unsigned taddr, float (&v)[32]) {
-  unsigned r[32];
+// A from tensor memory (row = lane, two bfloat16 a column), B from shared memory
+__device__ __forceinline__ void umma_ts(unsigned d_tmem, unsigned a_tmem, unsigned long long b_desc, unsigned id, unsigned accumulate) {
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+               "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+               ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(id), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32_issue(unsigned taddr, unsigned (&r)[32]) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
                "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
@@ -116,12 +131,29 @@ __device__ __forceinline__ void tmem_ld32(unsigned taddr, float (&v)[32]) {
                  "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
                  "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                : "r"(taddr));
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st32(unsigned taddr, const unsigned (&r)[32]) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+               "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31};"
+               ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                 "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+                 "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+                 "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]),
+                 "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 pk = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&pk);
 }
 
-__global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(
+__global__ void __launch_bounds__(THREADS, 2) attn_prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q,   // [tokens, heads, D], box 64 x 1 x 128
     const __grid_constant__ CUtensorMap map_k,   // [pages * kv heads * 64, D], box 64 x 64
     const __grid_constant__ CUtensorMap map_v,
@@ -130,17 +162,19 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(
     float scale_log2, int window, int* err) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  unsigned char* q_s = base;                                   // [DA][128][64]
-  unsigned char* kv_s = q_s + Q_BYTES;                         // [stages][K: DA atoms | V: DA atoms]
-  unsigned char* p_s = kv_s + KV_STAGES * (K_BYTES + V_BYTES); // [128][64]
-  unsigned long long* bars = reinterpret_cast<unsigned long long*>(p_s + P_BYTES);
-  unsigned long long* q_full = bars;          // TMA -> driver
-  unsigned long long* kv_full = bars + 1;     // [2] TMA -> driver
-  unsigned long long* kv_free = bars + 3;     // [2] MMA done -> driver
-  unsigned long long* s_done = bars + 5;      // MMA done -> softmax warps
-  unsigned long long* p_ready = bars + 6;     // softmax warps (128 arrivals) -> driver
-  unsigned long long* t_done = bars + 7;      // MMA done -> softmax warps
-  unsigned* tmem_slot = reinterpret_cast<unsigned*>(bars + 8);
+  unsigned char* q_s = base;                        // [DA][128][64]
+  unsigned char* k_s = q_s + Q_BYTES;               // [stages][DA][64][64]
+  unsigned char* v_s = k_s + STAGES * K_BYTES;      // [stages][DA][64][64]
+  unsigned long long* bars = reinterpret_cast<unsigned long long*>(v_s + STAGES * V_BYTES);
+  unsigned long long* q_full = bars;                    // TMA -> MMA
+  unsigned long long* k_full = bars + 1;                // [stages] TMA -> MMA
+  unsigned long long* k_free = k_full + STAGES;         // [stages] S product done -> TMA
+  unsigned long long* v_full = k_free + STAGES;         // [stages] TMA -> MMA
+  unsigned long long* v_free = v_full + STAGES;         // [stages] P V product done -> TMA
+  unsigned long long* s_full = v_free + STAGES;         // [2] S product done -> softmax warps
+  unsigned long long* p_ready = s_full + 2;             // [2] softmax warps (128 arrivals) -> MMA
+  unsigned long long* o_done = p_ready + 2;             // P V product done -> softmax warps
+  unsigned* tmem_slot = reinterpret_cast<unsigned*>(o_done + 1);
   __shared__ int failed_s;
   volatile int* failed = &failed_s;
 
@@ -158,13 +192,14 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(
   if (threadIdx.x == 0) {
     failed_s = 0;
     mbar_init(q_full, 1);
-    for (int s = 0; s < KV_STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_free[s], 1); }
-    mbar_init(s_done, 1);
-    mbar_init(p_ready, BM);
-    mbar_init(t_done, 1);
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&k_full[s], 1); mbar_init(&k_free[s], 1); mbar_init(&v_full[s], 1); mbar_init(&v_free[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) { mbar_init(&s_full[b], 1); mbar_init(&p_ready[b], BM); }
+    mbar_init(o_done, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 4) {
+  if (warp == 5) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
@@ -175,144 +210,187 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(
 
   if (warp == 4) {
     if (lane == 0) {
-      // ---- driver: TMA and MMA ----
-      auto load_kv = [&](int j) {
-        const int s = j % KV_STAGES;
-        unsigned char* ks = kv_s + (size_t)s * (K_BYTES + V_BYTES);
-        unsigned char* vs = ks + K_BYTES;
+      // ---- TMA: Q, then K one tile ahead of V, in the order the products use them ----
+      auto load_k = [&](int j) {
+        const int s = j % STAGES;
+        unsigned char* ks = k_s + (size_t)s * K_BYTES;
         const int row0 = (pt[pg_first + j] * nKV + kvh) * BN;
-        mbar_expect_tx(&kv_full[s], K_BYTES + V_BYTES);
+        mbar_expect_tx(&k_full[s], K_BYTES);
 #pragma unroll
-        for (int a = 0; a < DA; ++a) {
-          tma_load_2d(ks + a * KV_ATOM, &map_k, a * 64, row0, &kv_full[s]);
-          tma_load_2d(vs + a * KV_ATOM, &map_v, a * 64, row0, &kv_full[s]);
-        }
+        for (int a = 0; a < DA; ++a) tma_load_2d(ks + a * KV_ATOM, &map_k, a * 64, row0, &k_full[s]);
+      };
+      auto load_v = [&](int j) {
+        const int s = j % STAGES;
+        unsigned char* vs = v_s + (size_t)s * V_BYTES;
+        const int row0 = (pt[pg_first + j] * nKV + kvh) * BN;
+        mbar_expect_tx(&v_full[s], V_BYTES);
+#pragma unroll
+        for (int a = 0; a < DA; ++a) tma_load_2d(vs + a * KV_ATOM, &map_v, a * 64, row0, &v_full[s]);
       };
       mbar_expect_tx(q_full, Q_BYTES);
 #pragma unroll
       for (int a = 0; a < DA; ++a) tma_load_3d(q_s + a * Q_ATOM, &map_q, a * 64, h, tok0, q_full);
-      load_kv(0);
-      bool ok = mbar_wait(q_full, 0, err, failed);
-      constexpr unsigned ID_S = idesc(BM, BN, 0);   // S[128 x 64]  = Q (K-major) x K (K-major)
-      constexpr unsigned ID_T = idesc(BM, D, 1);    // T[128 x D]   = P (K-major) x V (MN-major)
+      load_k(0);
+      bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
-        const int s = j % KV_STAGES;
         if (j + 1 < n_tiles) {
-          // the other stage is free once the P V product of tile j-1 has read it
-          if (j >= 1) ok = mbar_wait(&kv_free[(j + 1) % KV_STAGES], (unsigned)(((j - 1) / KV_STAGES) & 1), err, failed);
+          if (j + 1 >= STAGES) ok = mbar_wait(&k_free[(j + 1) % STAGES], (unsigned)((((j + 1) / STAGES) - 1) & 1), err, failed);
           if (!ok) break;
-          load_kv(j + 1);
+          load_k(j + 1);
         }
-        ok = mbar_wait(&kv_full[s], (unsigned)((j / KV_STAGES) & 1), err, failed);
+        if (j >= STAGES) ok = mbar_wait(&v_free[j % STAGES], (unsigned)(((j / STAGES) - 1) & 1), err, failed);
         if (!ok) break;
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const unsigned char* ks = kv_s + (size_t)s * (K_BYTES + V_BYTES);
-        const unsigned char* vs = ks + K_BYTES;
-        // S = Q K^T: k steps of 16 along the head size; 4 steps per 64-wide atom, 32 bytes apart
+        load_v(j);
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      // ---- tcgen05.mma: S one tile ahead, O += P V behind the softmax ----
+      constexpr unsigned ID_S = idesc(BM, BN, 0);   // S[128 x 64]  = Q (K-major) x K (K-major)
+      constexpr unsigned ID_O = idesc(BM, D, 1);    // O[128 x D]  += P (tensor memory) x V (MN-major)
+      auto issue_s = [&](int j) {
+        const unsigned char* ks = k_s + (size_t)(j % STAGES) * K_BYTES;
+        // k steps of 16 along the head size; 4 steps per 64-wide atom, 32 bytes apart
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const unsigned long long a_desc = umma_desc(q_s + (kk / 4) * Q_ATOM + (kk % 4) * 32, 16, 1024);
           const unsigned long long b_desc = umma_desc(ks + (kk / 4) * KV_ATOM + (kk % 4) * 32, 16, 1024);
-          umma(tmem, a_desc, b_desc, ID_S, kk != 0);
+          umma(tmem + (unsigned)((j & 1) * S_COL), a_desc, b_desc, ID_S, kk != 0);
         }
-        umma_commit(s_done);
-        // T = P V once P is in shared memory: k steps of 16 keys = two 8-row swizzle groups = 2048 bytes;
-        // V is MN-major: 64 d contiguous per row, the next 64-wide atom KV_ATOM bytes on (leading offset)
-        ok = mbar_wait(p_ready, (unsigned)(j & 1), err, failed);
+        umma_commit(&s_full[j & 1]);
+        umma_commit(&k_free[j % STAGES]);
+      };
+      bool ok = mbar_wait(q_full, 0, err, failed);
+      if (ok) ok = mbar_wait(&k_full[0], 0, err, failed);
+      if (ok) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        issue_s(0);
+      }
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        if (j + 1 < n_tiles) {
+          // S of the next tile goes into the other buffer: the P V product that read it was issued before
+          ok = mbar_wait(&k_full[(j + 1) % STAGES], (unsigned)(((j + 1) / STAGES) & 1), err, failed);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          issue_s(j + 1);
+        }
+        ok = mbar_wait(&v_full[j % STAGES], (unsigned)((j / STAGES) & 1), err, failed);
+        if (ok) ok = mbar_wait(&p_ready[j & 1], (unsigned)((j >> 1) & 1), err, failed);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const unsigned char* vs = v_s + (size_t)(j % STAGES) * V_BYTES;
+        // k steps of 16 keys: 8 columns of P; in V two 8-row swizzle groups = 2048 bytes; V is MN-major:
+        // 64 d contiguous per key, the next 64-wide atom KV_ATOM bytes on (leading offset)
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk) {
-          const unsigned long long a_desc = umma_desc(p_s + kk * 32, 16, 1024);
           const unsigned long long b_desc = umma_desc(vs + kk * 2048, KV_ATOM, 1024);
-          umma(tmem + T_COL, a_desc, b_desc, ID_T, kk != 0);
+          umma_ts(tmem + O_COL, tmem + (unsigned)((j & 1) * S_COL + kk * 8), b_desc, ID_O, (j > 0 || kk > 0) ? 1u : 0u);
         }
-        umma_commit(t_done);
-        umma_commit(&kv_free[s]);
+        umma_commit(&v_free[j % STAGES]);
+        umma_commit(o_done);
       }
     }
   } else {
-    // ---- softmax and accumulation: one thread per query row ----
+    // ---- softmax: one thread per query row ----
     const int r = warp * 32 + lane;                       // tile row = TMEM lane
     const int qpos = pos0 + r;
     const unsigned lane_base = tmem + ((unsigned)(warp * 32) << 16);
-    float o[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) o[i] = 0.f;
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      ok = mbar_wait(s_done, (unsigned)(j & 1), err, failed);
+    for (int j = 0; j < n_tiles; ++j) {
+      ok = mbar_wait(&s_full[j & 1], (unsigned)((j >> 1) & 1), err, failed);
+      ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const unsigned s_addr = lane_base + (unsigned)((j & 1) * S_COL);
       const int key0 = (pg_first + j) * BN;
       float sc[BN];
       {
-        float v[32];
-        tmem_ld32(lane_base, v);
+        unsigned r0[32], r1[32];
+        tmem_ld32_issue(s_addr, r0);
+        tmem_ld32_issue(s_addr + 32, r1);
+        tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) sc[i] = v[i];
-        tmem_ld32(lane_base + 32, v);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) sc[32 + i] = v[i];
+        for (int i = 0; i < 32; ++i) { sc[i] = __uint_as_float(r0[i]); sc[32 + i] = __uint_as_float(r1[i]); }
       }
+      // only tiles that reach the diagonal or the window's far edge need a mask (uniform for the block)
+      const bool masked = (key0 + BN - 1 > pos0) || (window > 0 && pos0 + BM - 1 - key0 >= window);
       float mx = -INFINITY;
+      if (masked) {
 #pragma unroll
-      for (int i = 0; i < BN; ++i) {
-        const int kp = key0 + i;
-        bool vis = kp <= qpos;
-        if (window > 0) vis = vis && (qpos - kp < window);
-        sc[i] = vis ? sc[i] * scale_log2 : -INFINITY;
-        mx = fmaxf(mx, sc[i]);
-      }
-      const float m_new = fmaxf(m_run, mx);
-      const float m_use = m_new == -INFINITY ? 0.f : m_new;
-      const float alpha = exp2f(m_run - m_use);
-      m_run = m_new;
-      float sum = 0.f;
-      // P, rounded to bfloat16, into the swizzled K-major tile: row r, 16-byte chunk c at (c ^ (r & 7))
-      unsigned char* prow = p_s + (size_t)r * 128;
-#pragma unroll
-      for (int c = 0; c < BN / 8; ++c) {
-        unsigned w4[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float p0 = exp2f(sc[c * 8 + 2 * e] - m_use), p1 = exp2f(sc[c * 8 + 2 * e + 1] - m_use);
-          sum += p0 + p1;
-          __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
-          w4[e] = *reinterpret_cast<unsigned*>(&pk);
+        for (int i = 0; i < BN; ++i) {
+          const int kp = key0 + i;
+          bool vis = kp <= qpos;
+          if (window > 0) vis = vis && (qpos - kp < window);
+          sc[i] = vis ? sc[i] : -INFINITY;
+          mx = fmaxf(mx, sc[i]);
         }
-        *reinterpret_cast<uint4*>(prow + ((c ^ (r & 7)) * 16)) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < BN; ++i) mx = fmaxf(mx, sc[i]);
       }
+      const float m_new = fmaxf(m_run, mx * scale_log2);
+      float alpha = 1.f;
+      if (__any_sync(0xffffffffu, m_new - m_run > GROW)) {
+        // some row's maximum grew by much: every row of the warp takes its exact maximum and rescales
+        alpha = m_new == -INFINITY ? 1.f : fast_exp2(m_run - m_new);
+        m_run = m_new;
+        if (j > 0) {
+          ok = mbar_wait(o_done, (unsigned)((j - 1) & 1), err, failed);   // O holds tiles 0 .. j-1
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+          for (int c = 0; c < D; c += 32) {
+            unsigned v[32];
+            tmem_ld32_issue(lane_base + O_COL + c, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+            tmem_st32(lane_base + O_COL + c, v);
+          }
+        }
+      }
+      const float m_use = m_run == -INFINITY ? 0.f : m_run;
+      float sum = 0.f;
+      unsigned pk[32];
+#pragma unroll
+      for (int i = 0; i < BN / 2; ++i) {
+        const float p0 = fast_exp2(fmaf(sc[2 * i], scale_log2, -m_use));
+        const float p1 = fast_exp2(fmaf(sc[2 * i + 1], scale_log2, -m_use));
+        sum += p0 + p1;
+        pk[i] = pack_bf16(p0, p1);
+      }
+      tmem_st32(s_addr, pk);   // P over the first half of its own S buffer
+      tmem_st_wait();
       l_run = l_run * alpha + sum;
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P is read by the tensor core (async proxy)
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      mbar_arrive(p_ready);
-      // T = P V of this tile -> O = O * alpha + T
-      ok = mbar_wait(t_done, (unsigned)(j & 1), err, failed);
-      if (!ok) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll
-      for (int c = 0; c < D; c += 32) {
-        float v[32];
-        tmem_ld32(lane_base + T_COL + c, v);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c + i] = fmaf(o[c + i], alpha, v[i]);
-      }
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      mbar_arrive(&p_ready[j & 1]);
     }
-    if (ok && r < rows) {
+    if (ok) {
+      ok = mbar_wait(o_done, (unsigned)((n_tiles - 1) & 1), err, failed);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
       bf16* dst = out + ((size_t)(tok0 + r) * nH + h) * D;
 #pragma unroll
-      for (int c = 0; c < D; c += 8) {
-        unsigned w4[4];
+      for (int c = 0; c < D; c += 32) {
+        unsigned v[32];
+        tmem_ld32_issue(lane_base + O_COL + c, v);
+        tmem_ld_wait();
+        if (r < rows) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          __nv_bfloat162 pk = __floats2bfloat162_rn(o[c + 2 * e] * inv, o[c + 2 * e + 1] * inv);
-          w4[e] = *reinterpret_cast<unsigned*>(&pk);
+          for (int i = 0; i < 32; i += 8) {
+            uint4 w;
+            w.x = pack_bf16(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
+            w.y = pack_bf16(__uint_as_float(v[i + 2]) * inv, __uint_as_float(v[i + 3]) * inv);
+            w.z = pack_bf16(__uint_as_float(v[i + 4]) * inv, __uint_as_float(v[i + 5]) * inv);
+            w.w = pack_bf16(__uint_as_float(v[i + 6]) * inv, __uint_as_float(v[i + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + c + i) = w;
+          }
         }
-        *reinterpret_cast<uint4*>(dst + c) = make_uint4(w4[0], w4[1], w4[2], w4[3]);
       }
     }
   }
@@ -323,12 +401,14 @@ __global__ void __launch_bounds__(THREADS, 1) attn_prefill_tc_kernel(
     // a wait ran out: give copies that may still be in flight a bounded time to land
     if (threadIdx.x == 0) {
       const long long t0 = clock64();
-      for (int s = 0; s < KV_STAGES; ++s)
-        while (!mbar_try_wait(&kv_full[s], 0) && !mbar_try_wait(&kv_full[s], 1) && clock64() - t0 < WAIT_CYCLES) {}
+      for (int s = 0; s < STAGES; ++s) {
+        while (!mbar_try_wait(&k_full[s], 0) && !mbar_try_wait(&k_full[s], 1) && clock64() - t0 < WAIT_CYCLES) {}
+        while (!mbar_try_wait(&v_full[s], 0) && !mbar_try_wait(&v_full[s], 1) && clock64() - t0 < WAIT_CYCLES) {}
+      }
     }
     __syncthreads();
   }
-  if (warp == 4) {
+  if (warp == 5) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
   }

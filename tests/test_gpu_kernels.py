@@ -534,6 +534,48 @@ def test_attn_prefill_tc(n_heads, n_kv, d, window):
     torch.testing.assert_close(out.cpu().float(), torch.stack(refs), rtol=2e-2, atol=2e-2)
 
 
+@pytest.mark.parametrize("where", ["early", "late", "steps"])
+def test_attn_prefill_tc_running_maximum(where):
+    """The tcgen05 kernel keeps a running maximum that moves only on large growth and rescales O in tensor
+    memory then.  One key that stands out early (no later growth), one that stands out late (O is
+    rescaled after hundreds of keys), and key sizes that rise in steps (growth below and above the
+    threshold, tile after tile) must all give plain attention's result."""
+    k = K()
+    dtype = torch.bfloat16
+    n_heads, n_kv, d, page, tile = 4, 2, 128, 64, 128
+    L = 450
+    scale = 1.0 / math.sqrt(d)
+    g = torch.Generator().manual_seed(11)
+    keys = torch.randn(L, n_kv, d, generator=g)
+    vals = torch.randn(L, n_kv, d, generator=g)
+    q = torch.randn(L, n_heads, d, generator=g)
+    if where == "steps":
+        keys *= (0.25 * (1 + torch.arange(L) // 64)).view(L, 1, 1) * 2.0
+    else:
+        at = 3 if where == "early" else 389
+        keys[at] = 0
+        keys[at, :, 0] = 24.0
+        q[:, :, 0] = 20.0   # score 480 * scale = 42 above the rest at that key
+        vals[at] = 5.0
+    seqs = {1: (keys.to(dtype), vals.to(dtype))}
+    kc, vc, pt = _fill_cache(seqs, n_kv, d, page, dtype, n_pages=12, max_pages=8, slots=2, scatter_seed=3)
+    qb = q.to(dtype)
+    refs = [_attn_ref(qb[i], seqs[1][0], seqs[1][1], i, scale, None) for i in range(L)]
+    tiles0 = list(range(0, L, tile))
+    tilesn = [min(tile, L - t) for t in tiles0]
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    out = torch.full((L, n_heads * d), 9.0, device=DEV, dtype=dtype)
+    k.attn_prefill_tc(qb.to(DEV), kc, vc, pt, i32(tiles0), i32(tilesn), i32([1] * L), i32(list(range(L))), out,
+                      len(tiles0), scale, None)
+    torch.cuda.synchronize()
+    k.check_error_flags()
+    ref = torch.stack(refs)
+    if where != "steps":
+        at = 3 if where == "early" else 389
+        assert (ref[at + 5:, :] - 5.0).abs().max() < 0.05   # the marked key takes all the weight after it
+    torch.testing.assert_close(out.cpu().float(), ref, rtol=2e-2, atol=2e-2)
+
+
 # ------------------------------------------------------------------------------------ token choice
 def test_argmax_rows_ties_and_state():
     k = K()
