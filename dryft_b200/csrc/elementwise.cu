@@ -184,10 +184,65 @@ __global__ void rmsnorm_kernel(const T* x, const T* __restrict__ delta, const fl
   }
 }
 
+
+// Many rows at once (a prompt): small blocks, so that every row of the step is in flight together, and
+// the summed row stays in registers (up to RMS_REG_VECS 16-byte vectors a thread) instead of shared memory.
+constexpr int RMS_REG_VECS = 4;
+template <typename T>
+__global__ void rmsnorm_rows_kernel(const T* x, const T* __restrict__ delta, const float* __restrict__ w,
+                                    const int* __restrict__ rows, T* x_out, T* __restrict__ h, int hidden, float eps) {
+  __shared__ float scratch[33];
+  constexpr int V = Vec16<T>::N;
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  const T* xr = x + (size_t)src * hidden;
+  const T* dr = delta ? delta + (size_t)src * hidden : nullptr;
+  T* xo = x_out ? x_out + (size_t)src * hidden : nullptr;
+  T* hr = h + (size_t)r * hidden;
+  float v[RMS_REG_VECS][V];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < RMS_REG_VECS; ++k) {
+    const int i = (threadIdx.x + k * blockDim.x) * V;
+    if (i < hidden) {
+      load_vec<T>(xr + i, v[k]);
+      if (dr) {
+        float d[V];
+        load_vec<T>(dr + i, d);
+#pragma unroll
+        for (int e = 0; e < V; ++e) v[k][e] = rnd<T>(v[k][e] + d[e]);
+      }
+#pragma unroll
+      for (int e = 0; e < V; ++e) ss += v[k][e] * v[k][e];
+    }
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)hidden + eps);
+#pragma unroll
+  for (int k = 0; k < RMS_REG_VECS; ++k) {
+    const int i = (threadIdx.x + k * blockDim.x) * V;
+    if (i < hidden) {
+      float o[V];
+#pragma unroll
+      for (int e = 0; e < V; ++e) o[e] = w[i + e] * rnd<T>(v[k][e] * inv);
+      if (xo) store_vec<T>(xo + i, v[k]);
+      store_vec<T>(hr + i, o);
+    }
+  }
+}
+
 template <typename T>
 static int rmsnorm_launch(const void* x, const void* delta, const float* w, const int* rows, void* x_out, void* h,
                           int n_rows, int hidden, float eps, cudaStream_t st) {
   if (n_rows <= 0) return 0;
+  constexpr int V = Vec16<T>::N;
+  if (n_rows >= 256 && hidden % V == 0 && hidden / V <= RMS_REG_VECS * 1024) {
+    const int vecs = hidden / V;
+    int threads = ((vecs + RMS_REG_VECS - 1) / RMS_REG_VECS + 31) & ~31;
+    if (threads < 64) threads = 64;
+    rmsnorm_rows_kernel<T><<<n_rows, threads, 0, st>>>((const T*)x, (const T*)delta, w, rows, (T*)x_out, (T*)h, hidden, eps);
+    return launch_status();
+  }
   size_t smem = (size_t)(((hidden + 3) & ~3) + 33) * sizeof(float);
   if (smem > 200 * 1024) return DRYFT_ERR_UNSUPPORTED;
   static size_t attr_bytes = 48 * 1024;  // per instantiation; raised by an eager launch before any capture

@@ -14,6 +14,10 @@
 //   o[j+R/2]   = T( T(n[j+R/2]*c)   + T(n[j]*s) )
 // R (rotary_dim) may be smaller than the head size: the remaining dims pass through after the
 // norm.  R = 0 disables the rotation; has_norm = 0 disables the norm.
+//
+// c and s depend on the token only, not on the layer: a step with many tokens evaluates them once
+// (rope_table_kernel: [token][cos | sin][R/2], already rounded to T) and every layer's launch reads
+// the table; without a table each warp evaluates its own.
 #include "common.cuh"
 
 // two consecutive elements of T <-> two floats
@@ -44,18 +48,19 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) qk_norm_rope_store_kernel(
     const T* __restrict__ qkv, int qkv_stride,                 // [N, qkv_stride]; q | k | v column blocks
     const float* __restrict__ wq, const float* __restrict__ wk,  // [D] each (ignored if !has_norm)
     const float* __restrict__ inv_freq,                         // [R/2]
+    const T* __restrict__ cs_table,                             // [N][2][R/2] cos | sin of each token, or null
     const int* __restrict__ tok_slot, const int* __restrict__ tok_pos,
     T* __restrict__ q_out,                                      // [N, nH, D]
     T* __restrict__ k_pages, T* __restrict__ v_pages,           // [pages, nKV, page_size, D]
     const int* __restrict__ page_table, int max_pages,
     int n_tokens, int nH, int nKV, int D, int R, int page_size, float eps, int has_norm, int write_kv) {
-  // a warp per (token, head): plenty of warps in flight hide the latency of the few loads each one has
+  // a warp per (token, head): plenty of warps in flight hide the latency of the few loads each one has;
+  // grid (tokens, groups of ROPE_WARPS heads)
   const int lane = threadIdx.x & 31;
   const int heads_total = nH + (write_kv ? 2 * nKV : 0);
-  const long long item = (long long)blockIdx.x * ROPE_WARPS + (threadIdx.x >> 5);
-  if (item >= (long long)n_tokens * heads_total) return;
-  const int n = (int)(item / heads_total);
-  const int head0 = (int)(item - (long long)n * heads_total);
+  const int n = blockIdx.x;
+  const int head0 = blockIdx.y * ROPE_WARPS + (threadIdx.x >> 5);
+  if (head0 >= heads_total) return;
   const int slot = tok_slot[n];
   const int pos = tok_pos[n];
   const int half = R >> 1;
@@ -67,6 +72,17 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) qk_norm_rope_store_kernel(
   float cs[MAX_PAIRS2][2], sn[MAX_PAIRS2][2];
 #pragma unroll
   for (int i = 0; i < MAX_PAIRS2; ++i) {
+    if (cs_table != nullptr && (half & 1) == 0) {
+      const int j = 2 * lane + 64 * i;
+      cs[i][0] = cs[i][1] = 1.f;
+      sn[i][0] = sn[i][1] = 0.f;
+      if (j < half && head0 < nH + nKV && slot >= 0) {
+        const T* row = cs_table + (size_t)n * R;
+        load2<T>(row + j, cs[i][0], cs[i][1]);
+        load2<T>(row + half + j, sn[i][0], sn[i][1]);
+      }
+      continue;
+    }
 #pragma unroll
     for (int e = 0; e < 2; ++e) {
       const int j = 2 * lane + 64 * i + e;
@@ -189,29 +205,54 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) qk_norm_rope_store_kernel(
   }
 }
 
+// cos / sin of every token's angles, rounded to T: table [n_tokens][2][half]
 template <typename T>
-static int launch(const void* qkv, int qkv_stride, const float* wq, const float* wk, const float* inv_freq,
+__global__ void rope_table_kernel(const int* __restrict__ tok_pos, const float* __restrict__ inv_freq, T* __restrict__ table,
+                                  int n_tokens, int half) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)n_tokens * half) return;
+  const int n = (int)(i / half), j = (int)(i - (long long)n * half);
+  float s_, c_;
+  sincosf((float)tok_pos[n] * inv_freq[j], &s_, &c_);
+  table[(size_t)n * 2 * half + j] = from_f32<T>(c_);
+  table[(size_t)n * 2 * half + half + j] = from_f32<T>(s_);
+}
+
+DRYFT_API int dryft_rope_table(int is_bf16, const int* tok_pos, const float* inv_freq, void* table, int n_tokens, int R,
+                               cudaStream_t st) {
+  if (n_tokens <= 0 || R <= 0) return 0;
+  if (R & 1) return DRYFT_ERR_UNSUPPORTED;
+  const int half = R / 2;
+  const long long items = (long long)n_tokens * half;
+  const unsigned blocks = (unsigned)((items + 255) / 256);
+  if (is_bf16) rope_table_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(tok_pos, inv_freq, (__nv_bfloat16*)table, n_tokens, half);
+  else rope_table_kernel<float><<<blocks, 256, 0, st>>>(tok_pos, inv_freq, (float*)table, n_tokens, half);
+  return launch_status();
+}
+
+template <typename T>
+static int launch(const void* qkv, int qkv_stride, const float* wq, const float* wk, const float* inv_freq, const void* cs_table,
                   const int* tok_slot, const int* tok_pos, void* q_out, void* k_pages, void* v_pages,
                   const int* page_table, int max_pages, int n_tokens, int nH, int nKV, int D, int R, int page_size,
                   float eps, int has_norm, int write_kv, cudaStream_t st) {
   if (n_tokens <= 0) return 0;
   if (D <= 0 || (R & 1) || R > D || R < 0) return DRYFT_ERR_UNSUPPORTED;
-  const long long items = (long long)n_tokens * (nH + (write_kv ? 2 * nKV : 0));
-  const long long blocks = (items + ROPE_WARPS - 1) / ROPE_WARPS;
-  if (blocks > 0x7fffffffLL) return DRYFT_ERR_UNSUPPORTED;
-  qk_norm_rope_store_kernel<T><<<(unsigned)blocks, ROPE_WARPS * 32, 0, st>>>(
-      (const T*)qkv, qkv_stride, wq, wk, inv_freq, tok_slot, tok_pos, (T*)q_out, (T*)k_pages, (T*)v_pages, page_table,
+  const int heads_total = nH + (write_kv ? 2 * nKV : 0);
+  const int head_groups = (heads_total + ROPE_WARPS - 1) / ROPE_WARPS;
+  if (head_groups > 65535) return DRYFT_ERR_UNSUPPORTED;
+  qk_norm_rope_store_kernel<T><<<dim3((unsigned)n_tokens, (unsigned)head_groups), ROPE_WARPS * 32, 0, st>>>(
+      (const T*)qkv, qkv_stride, wq, wk, inv_freq, (const T*)cs_table, tok_slot, tok_pos, (T*)q_out, (T*)k_pages, (T*)v_pages, page_table,
       max_pages, n_tokens, nH, nKV, D, R, page_size, eps, has_norm, write_kv);
   return launch_status();
 }
 
 DRYFT_API int dryft_qk_norm_rope_store(int is_bf16, const void* qkv, int qkv_stride, const float* wq, const float* wk,
-                                       const float* inv_freq, const int* tok_slot, const int* tok_pos, void* q_out,
+                                       const float* inv_freq, const void* cs_table, const int* tok_slot, const int* tok_pos, void* q_out,
                                        void* k_pages, void* v_pages, const int* page_table, int max_pages, int n_tokens,
                                        int nH, int nKV, int D, int R, int page_size, float eps, int has_norm,
                                        int write_kv, cudaStream_t st) {
-  return is_bf16 ? launch<__nv_bfloat16>(qkv, qkv_stride, wq, wk, inv_freq, tok_slot, tok_pos, q_out, k_pages, v_pages,
+  return is_bf16 ? launch<__nv_bfloat16>(qkv, qkv_stride, wq, wk, inv_freq, cs_table, tok_slot, tok_pos, q_out, k_pages, v_pages,
                                          page_table, max_pages, n_tokens, nH, nKV, D, R, page_size, eps, has_norm, write_kv, st)
-                 : launch<float>(qkv, qkv_stride, wq, wk, inv_freq, tok_slot, tok_pos, q_out, k_pages, v_pages,
+                 : launch<float>(qkv, qkv_stride, wq, wk, inv_freq, cs_table, tok_slot, tok_pos, q_out, k_pages, v_pages,
                                  page_table, max_pages, n_tokens, nH, nKV, D, R, page_size, eps, has_norm, write_kv, st);
 }

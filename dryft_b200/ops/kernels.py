@@ -56,15 +56,16 @@ def core() -> ctypes.CDLL:
             lib.dryft_rmsnorm.argtypes = [_i, _p, _p, _p, _p, _p, _p, _i, _i, _f, _p]
             lib.dryft_residual_add.argtypes = [_i, _p, _p, _ll, _p]
             lib.dryft_silu_mul.argtypes = [_i, _p, _p, _i, _i, _p]
-            lib.dryft_qk_norm_rope_store.argtypes = [_i, _p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i,
+            lib.dryft_qk_norm_rope_store.argtypes = [_i, _p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i,
                                                      _i, _i, _f, _i, _i, _p]
+            lib.dryft_rope_table.argtypes = [_i, _p, _p, _p, _i, _i, _p]
             lib.dryft_gemm_nt_f32.argtypes = [_p, _i, _p, _p, _i, _i, _i, _i, _p]
             lib.dryft_argmax_rows.argtypes = [_p, _i, _i, _ll, _p, _p, _p, _p]
             lib.dryft_sample_rows.argtypes = [_p, _i, _i, _ll, _f, _i, _ull, _p, _p, _i, _p, _p, _p, _p]
             lib.dryft_gemm_small_m.argtypes = [_p, _i, _p, _p, _i, _i, _i, _i, _i, _p, _p, _i, _f, _p, _i, _p]
             lib.dryft_row_sumsq.argtypes = [_p, _i, _i, _p, _p]
             for name in ("dryft_step_meta", "dryft_step_advance", "dryft_tokens_from_state", "dryft_embed",
-                         "dryft_rmsnorm", "dryft_residual_add", "dryft_silu_mul", "dryft_qk_norm_rope_store",
+                         "dryft_rmsnorm", "dryft_residual_add", "dryft_silu_mul", "dryft_qk_norm_rope_store", "dryft_rope_table",
                          "dryft_gemm_nt_f32", "dryft_argmax_rows", "dryft_sample_rows", "dryft_gemm_small_m", "dryft_row_sumsq"):
                 getattr(lib, name).restype = _i
             _core = lib
@@ -361,7 +362,9 @@ def silu_mul(gate_up, out) -> None:
 
 # ----------------------------------------------------------------------------- rope + cache write
 def qk_norm_rope_store(qkv, q_norm_w, k_norm_w, inv_freq, tok_slot, tok_pos, q_out, k_pages, v_pages, page_table,
-                       n_heads: int, n_kv_heads: int, head_dim: int, rotary_dim: int, eps: float, write_kv: bool = True) -> None:
+                       n_heads: int, n_kv_heads: int, head_dim: int, rotary_dim: int, eps: float, write_kv: bool = True,
+                       cs_table=None) -> None:
+    """``cs_table`` (from ``rope_table``; optional) holds the step's cos / sin so that layers share them."""
     n = qkv.shape[0]
     width = (n_heads + (2 * n_kv_heads if write_kv else 0)) * head_dim
     _need(qkv, "qkv", None, (n, width))
@@ -383,11 +386,28 @@ def qk_norm_rope_store(qkv, q_norm_w, k_norm_w, inv_freq, tok_slot, tok_pos, q_o
         _need(v_pages, "v_pages", qkv.dtype, tuple(k_pages.shape))
         _need(page_table, "page_table", torch.int32)
         page_size, max_pages = k_pages.shape[2], page_table.shape[1]
+    if cs_table is not None:
+        _need(cs_table, "cs_table", qkv.dtype, (None, 2, rotary_dim // 2))
+        if cs_table.shape[0] < n:
+            raise KernelError("qk_norm_rope_store: cos/sin table shorter than the batch")
     _ok(core().dryft_qk_norm_rope_store(is_bf16, _ptr(qkv), width, _ptr(q_norm_w), _ptr(k_norm_w), _ptr(inv_freq),
-                                        _ptr(tok_slot), _ptr(tok_pos), _ptr(q_out), _ptr(k_pages if write_kv else None),
+                                        _ptr(cs_table), _ptr(tok_slot), _ptr(tok_pos), _ptr(q_out), _ptr(k_pages if write_kv else None),
                                         _ptr(v_pages if write_kv else None), _ptr(page_table if write_kv else None),
                                         max_pages, n, n_heads, n_kv_heads, head_dim, rotary_dim, page_size, float(eps),
                                         int(has_norm), int(write_kv), _stream()), "qk_norm_rope_store")
+
+
+def rope_table(tok_pos, inv_freq, n_tokens: int, dtype: torch.dtype) -> torch.Tensor:
+    """cos | sin of ``pos * inv_freq`` for every token of a step, rounded to ``dtype``: [n_tokens, 2, R/2]."""
+    _need(tok_pos, "tok_pos", torch.int32)
+    _need(inv_freq, "inv_freq", torch.float32)
+    if tok_pos.numel() < n_tokens:
+        raise KernelError("rope_table: tok_pos shorter than the batch")
+    half = inv_freq.numel()
+    table = torch.empty(n_tokens, 2, half, dtype=dtype, device=tok_pos.device)
+    is_bf16 = _act(table, "table")
+    _ok(core().dryft_rope_table(is_bf16, _ptr(tok_pos), _ptr(inv_freq), _ptr(table), n_tokens, 2 * half, _stream()), "rope_table")
+    return table
 
 
 # ----------------------------------------------------------------------------- attention

@@ -4,9 +4,11 @@
 ``inv_freq[j] = 1 / theta^(2j/R)`` for ``j = 0..R/2-1`` from ``arange(0, R, 2)`` int64 -> float32, angle
 ``pos * inv_freq[j]`` in 32-bit, cos/sin cast to the activation dtype, dims ``j`` and ``j + R/2``
 rotated together.  ``R`` (``rotary_dim``) may be smaller than the head size.  The angles and their
-cos/sin are evaluated inside the fused kernel (``csrc/rope_kv.cu``) from the position of each token;
-this part only owns ``inv_freq``, computed on the host with exactly the reference's expression so
-that the 32-bit products ``pos * inv_freq`` agree bit for bit with a table built the reference's way.
+cos/sin are evaluated on the device (``csrc/rope_kv.cu``) from the position of each token: inside the
+fused kernels for a decode step, and once per step into a table that all layers with the same
+``(theta, rotary_dim)`` share for a step of many tokens.  This part owns ``inv_freq``, computed on the
+host with exactly the reference's expression so that the 32-bit products ``pos * inv_freq`` agree bit
+for bit with a table built the reference's way.
 
 ``none``: no position encoding (``rotary_dim = 0``).
 """
@@ -17,7 +19,10 @@ from typing import Mapping, Optional
 
 import torch
 
-from .base import Runtime, register_position
+from ..ops import kernels as K
+from .base import Runtime, StepContext, register_position
+
+TABLE_MIN_TOKENS = 64   # below this every warp evaluates its own angles
 
 
 @register_position("rope")
@@ -30,6 +35,18 @@ class Rope:
         r = self.rotary_dim
         inv_freq = 1.0 / (self.theta ** (torch.arange(0, r, 2, dtype=torch.int64).to(torch.float32) / r))
         self.inv_freq: Optional[torch.Tensor] = inv_freq.to(rt.device)
+        self.dtype = rt.dtype
+
+    def table(self, ctx: StepContext) -> Optional[torch.Tensor]:
+        """The step's cos / sin table, made by the first layer that asks and kept in the step's context."""
+        if ctx.decode or ctx.n_tokens < TABLE_MIN_TOKENS:
+            return None
+        key = ("rope_table", self.theta, self.rotary_dim)
+        table = ctx.extras.get(key)
+        if table is None:
+            table = K.rope_table(ctx.tok_pos, self.inv_freq, ctx.n_tokens, self.dtype)
+            ctx.extras[key] = table
+        return table
 
 
 @register_position("none")
@@ -37,3 +54,6 @@ class NoPosition:
     def __init__(self, params: Mapping, head_dim: int, rt: Runtime):
         self.rotary_dim = 0
         self.inv_freq = None
+
+    def table(self, ctx: StepContext) -> None:
+        return None

@@ -68,7 +68,8 @@ def test_embed(dtype, hidden):
 
 # ------------------------------------------------------------------------------------ norms
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("rows,hidden,eps", [(1, 80, 1e-5), (7, 2560, 1e-6), (33, 200, 3e-6), (3, 13000, 1e-6)])
+@pytest.mark.parametrize("rows,hidden,eps", [(1, 80, 1e-5), (7, 2560, 1e-6), (33, 200, 3e-6), (3, 13000, 1e-6),
+                                             (300, 2560, 1e-6), (257, 72, 1e-5), (260, 5128, 1e-6)])
 def test_rmsnorm_plain_add_gather(dtype, rows, hidden, eps):
     k = K()
     x = (torch.randn(rows, hidden, device=DEV) * 3).to(dtype)
@@ -253,9 +254,12 @@ def _paged_cache(n_pages, n_kv, page, d, dtype, fill=0.0):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("with_table", [False, True])
 @pytest.mark.parametrize("n_heads,n_kv,d,rot,theta,eps", [(4, 2, 16, 16, 1e4, 1e-6), (6, 2, 48, 48, 5e5, 1e-5),
-                                                            (8, 8, 128, 128, 5e6, 1e-6), (3, 1, 64, 32, 1e4, 1e-6)])
-def test_qk_norm_rope_store(dtype, n_heads, n_kv, d, rot, theta, eps):
+                                                            (8, 8, 128, 128, 5e6, 1e-6), (3, 1, 64, 32, 1e4, 1e-6),
+                                                            (2, 1, 24, 18, 1e4, 1e-6)])
+def test_qk_norm_rope_store(dtype, with_table, n_heads, n_kv, d, rot, theta, eps):
+    """With the step's cos / sin table and with angles evaluated in the kernel: same result."""
     k = K()
     page, n_pages, max_pages, slots = 64, 9, 4, 3
     # tokens of two sequences at scattered positions (page boundaries 63/64, a far position)
@@ -272,7 +276,9 @@ def test_qk_norm_rope_store(dtype, n_heads, n_kv, d, rot, theta, eps):
     canary = 123.0
     kc, vc = _paged_cache(n_pages, n_kv, page, d, dtype, canary)
     q_out = torch.full((n, n_heads, d), canary, device=DEV).to(dtype)
-    k.qk_norm_rope_store(qkv, wq, wk, inv_freq, tok_slot, tok_pos, q_out, kc, vc, pt, n_heads, n_kv, d, rot, eps)
+    table = k.rope_table(tok_pos, inv_freq, n, dtype) if with_table else None
+    k.qk_norm_rope_store(qkv, wq, wk, inv_freq, tok_slot, tok_pos, q_out, kc, vc, pt, n_heads, n_kv, d, rot, eps,
+                         cs_table=table)
 
     # plain reference
     qc = qkv.cpu()
