@@ -291,6 +291,10 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ y, int
   float s = rnd<T>(g / (1.f + expf(-g)));
   y[i] = from_f32<T>(s * u);
 }
+// g / (1 + exp(-g)): exact division and exponential in the 32-bit path; where the result is rounded to
+// bfloat16 right away, the fast exponential and division (a few ulp of 32-bit) are far inside that rounding
+template <typename T> __device__ __forceinline__ float silu_f32(float g) { return g / (1.f + expf(-g)); }
+template <> __device__ __forceinline__ float silu_f32<__nv_bfloat16>(float g) { return __fdividef(g, 1.f + __expf(-g)); }
 // 16 bytes of gate and of up per thread (inter a multiple of the vector width)
 template <typename T>
 __global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ y, int inter, size_t total_vecs) {
@@ -305,7 +309,7 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ y,
   load_vec<T>(base + c, g);
   load_vec<T>(base + inter + c, u);
 #pragma unroll
-  for (int e = 0; e < V; ++e) o[e] = rnd<T>(g[e] / (1.f + expf(-g[e]))) * u[e];
+  for (int e = 0; e < V; ++e) o[e] = rnd<T>(silu_f32<T>(g[e])) * u[e];
   store_vec<T>(y + r * (size_t)inter + c, o);
 }
 template <typename T>

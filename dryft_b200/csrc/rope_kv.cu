@@ -205,6 +205,157 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) qk_norm_rope_store_kernel(
   }
 }
 
+
+// The common case (rotary size = head size, R/2 even and at most 64 * NP): a warp takes ROPE_HPW
+// consecutive heads of one token and issues every load of all of them before the first use, so that a
+// warp's life is one memory round trip, not one per head.  Grid (tokens, groups of heads).
+constexpr int ROPE_HPW = 4;
+template <typename T, int NP>
+__global__ void __launch_bounds__(ROPE_WARPS * 32) qk_norm_rope_store_fast_kernel(
+    const T* __restrict__ qkv, int qkv_stride, const float* __restrict__ wq, const float* __restrict__ wk,
+    const float* __restrict__ inv_freq, const T* __restrict__ cs_table, const int* __restrict__ tok_slot,
+    const int* __restrict__ tok_pos, T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages,
+    const int* __restrict__ page_table, int max_pages, int nH, int nKV, int D, int page_size, float eps, int has_norm,
+    int write_kv) {
+  const int lane = threadIdx.x & 31;
+  const int heads_total = nH + (write_kv ? 2 * nKV : 0);
+  const int n = blockIdx.x;
+  const int head_base = (blockIdx.y * ROPE_WARPS + (threadIdx.x >> 5)) * ROPE_HPW;
+  if (head_base >= heads_total) return;
+  const int half = D >> 1;
+  const T* row = qkv + (size_t)n * qkv_stride;
+  // every load that needs no other load first
+  float a[ROPE_HPW][NP][2], b[ROPE_HPW][NP][2];
+#pragma unroll
+  for (int u = 0; u < ROPE_HPW; ++u) {
+    const int head = min(head_base + u, heads_total - 1);   // the last warp may repeat a head; it is not stored twice
+#pragma unroll
+    for (int i = 0; i < NP; ++i) {
+      const int j = 2 * lane + 64 * i;
+      a[u][i][0] = a[u][i][1] = b[u][i][0] = b[u][i][1] = 0.f;
+      if (j < half) {
+        load2<T>(row + (size_t)head * D + j, a[u][i][0], a[u][i][1]);
+        load2<T>(row + (size_t)head * D + j + half, b[u][i][0], b[u][i][1]);
+      }
+    }
+  }
+  const int slot = tok_slot[n];
+  const int pos = tok_pos[n];
+  float cs[NP][2], sn[NP][2], wa[2][NP][2], wb[2][NP][2];
+#pragma unroll
+  for (int i = 0; i < NP; ++i) {
+    const int j = 2 * lane + 64 * i;
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      cs[i][e] = 1.f; sn[i][e] = 0.f;
+      wa[0][i][e] = wa[1][i][e] = wb[0][i][e] = wb[1][i][e] = 1.f;
+    }
+    if (j < half) {
+      if (cs_table != nullptr) {
+        load2<T>(cs_table + (size_t)n * D + j, cs[i][0], cs[i][1]);
+        load2<T>(cs_table + (size_t)n * D + half + j, sn[i][0], sn[i][1]);
+      }
+      if (has_norm) {
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          wa[0][i][e] = wq[j + e]; wb[0][i][e] = wq[j + e + half];
+          wa[1][i][e] = wk[j + e]; wb[1][i][e] = wk[j + e + half];
+        }
+      }
+    }
+  }
+  if (slot < 0) {
+    // padding token: a defined (zero) query, nothing cached
+#pragma unroll
+    for (int u = 0; u < ROPE_HPW; ++u) {
+      const int head = head_base + u;
+      if (head < nH)
+        for (int i = 2 * lane; i < D; i += 64) store2<T>(q_out + ((size_t)n * nH + head) * D + i, 0.f, 0.f);
+    }
+    return;
+  }
+  size_t page_off = 0;
+  if (write_kv)
+    page_off = ((size_t)page_table[(size_t)slot * max_pages + pos / page_size] * nKV * page_size + (pos % page_size)) * D;
+  if (cs_table == nullptr) {
+#pragma unroll
+    for (int i = 0; i < NP; ++i)
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int j = 2 * lane + 64 * i + e;
+        if (j < half) {
+          float s_, c_;
+          sincosf((float)pos * inv_freq[j], &s_, &c_);
+          cs[i][e] = rnd<T>(c_);
+          sn[i][e] = rnd<T>(s_);
+        }
+      }
+  }
+  // sums of squares of all heads together (value heads do not use theirs)
+  float inv[ROPE_HPW];
+#pragma unroll
+  for (int u = 0; u < ROPE_HPW; ++u) {
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NP; ++i)
+      ss += a[u][i][0] * a[u][i][0] + a[u][i][1] * a[u][i][1] + b[u][i][0] * b[u][i][0] + b[u][i][1] * b[u][i][1];
+    inv[u] = ss;
+  }
+  if (has_norm) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+      for (int u = 0; u < ROPE_HPW; ++u) inv[u] += __shfl_xor_sync(0xffffffffu, inv[u], o);
+#pragma unroll
+    for (int u = 0; u < ROPE_HPW; ++u) inv[u] = rsqrtf(inv[u] / (float)D + eps);
+  }
+#pragma unroll
+  for (int u = 0; u < ROPE_HPW; ++u) {
+    const int head = head_base + u;
+    if (head >= heads_total) break;
+    T* dst;
+    const bool is_q = head < nH;
+    if (is_q) {
+      dst = q_out + ((size_t)n * nH + head) * D;
+    } else {
+      const int kvh = (head - nH) % nKV;
+      const size_t off = page_off + (size_t)kvh * page_size * D;
+      if (head >= nH + nKV) {  // value head: plain copy
+#pragma unroll
+        for (int i = 0; i < NP; ++i) {
+          const int j = 2 * lane + 64 * i;
+          if (j < half) {
+            store2<T>(v_pages + off + j, a[u][i][0], a[u][i][1]);
+            store2<T>(v_pages + off + j + half, b[u][i][0], b[u][i][1]);
+          }
+        }
+        continue;
+      }
+      dst = k_pages + off;
+    }
+#pragma unroll
+    for (int i = 0; i < NP; ++i) {
+      const int j = 2 * lane + 64 * i;
+      if (j < half) {
+        float o1[2], o2[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          float x = a[u][i][e], y = b[u][i][e];
+          if (has_norm) {
+            x = rnd<T>(rnd<T>(x * inv[u]) * (is_q ? wa[0][i][e] : wa[1][i][e]));
+            y = rnd<T>(rnd<T>(y * inv[u]) * (is_q ? wb[0][i][e] : wb[1][i][e]));
+          }
+          // separate roundings of the two products, then of the sum (no fused multiply-add across them)
+          o1[e] = __fadd_rn(rnd<T>(__fmul_rn(x, cs[i][e])), -rnd<T>(__fmul_rn(y, sn[i][e])));
+          o2[e] = __fadd_rn(rnd<T>(__fmul_rn(y, cs[i][e])), rnd<T>(__fmul_rn(x, sn[i][e])));
+        }
+        store2<T>(dst + j, o1[0], o1[1]);
+        store2<T>(dst + j + half, o2[0], o2[1]);
+      }
+    }
+  }
+}
+
 // cos / sin of every token's angles, rounded to T: table [n_tokens][2][half]
 template <typename T>
 __global__ void rope_table_kernel(const int* __restrict__ tok_pos, const float* __restrict__ inv_freq, T* __restrict__ table,
@@ -238,6 +389,20 @@ static int launch(const void* qkv, int qkv_stride, const float* wq, const float*
   if (n_tokens <= 0) return 0;
   if (D <= 0 || (R & 1) || R > D || R < 0) return DRYFT_ERR_UNSUPPORTED;
   const int heads_total = nH + (write_kv ? 2 * nKV : 0);
+  if (R == D && (D & 3) == 0 && D <= 256) {
+    const int per_block = ROPE_WARPS * ROPE_HPW;
+    const dim3 grid((unsigned)n_tokens, (unsigned)((heads_total + per_block - 1) / per_block));
+    if (grid.y > 65535) return DRYFT_ERR_UNSUPPORTED;
+    if (D <= 128)
+      qk_norm_rope_store_fast_kernel<T, 1><<<grid, ROPE_WARPS * 32, 0, st>>>(
+          (const T*)qkv, qkv_stride, wq, wk, inv_freq, (const T*)cs_table, tok_slot, tok_pos, (T*)q_out, (T*)k_pages,
+          (T*)v_pages, page_table, max_pages, nH, nKV, D, page_size, eps, has_norm, write_kv);
+    else
+      qk_norm_rope_store_fast_kernel<T, 2><<<grid, ROPE_WARPS * 32, 0, st>>>(
+          (const T*)qkv, qkv_stride, wq, wk, inv_freq, (const T*)cs_table, tok_slot, tok_pos, (T*)q_out, (T*)k_pages,
+          (T*)v_pages, page_table, max_pages, nH, nKV, D, page_size, eps, has_norm, write_kv);
+    return launch_status();
+  }
   const int head_groups = (heads_total + ROPE_WARPS - 1) / ROPE_WARPS;
   if (head_groups > 65535) return DRYFT_ERR_UNSUPPORTED;
   qk_norm_rope_store_kernel<T><<<dim3((unsigned)n_tokens, (unsigned)head_groups), ROPE_WARPS * 32, 0, st>>>(
