@@ -35,8 +35,6 @@ typedef __nv_bfloat16 bf16;
 constexpr int D = DRYFT_HEAD_DIM;
 constexpr int G = DRYFT_GROUP;
 constexpr int PAGE = DRYFT_PAGE;
-constexpr int NWARP = 8;
-constexpr int THREADS = NWARP * 32;
 constexpr int SLICE = 16;                   // keys a warp handles at a time
 constexpr int SPP = PAGE / SLICE;           // slices per page
 constexpr int KS = D + 8;                   // padded row (elements): conflict-free ldmatrix
@@ -48,12 +46,18 @@ static_assert(PAGE % SLICE == 0, "page size must be a multiple of 16");
 // shared memory: Q [16][KS] bf16 and the new token's K and V rows, then per warp STAGES stages of
 // (K slice, V slice) [16][KS] bf16 each.
 // The combine buffers (m, l: [NWARP][16]; acc: [NWARP][G][D] floats) overlay the stages at the end.
-constexpr int STAGES = 2;                   // slices staged per warp (one in flight while one is used)
+// The block's shape is a template: NWARP warps with STAGES slices staged per warp (STAGES - 1 in flight
+// while one is used).  Few (row, kv head) pairs: wide blocks, one per SM, so that one sequence's keys
+// are walked by many warps.  Many pairs: narrow blocks with deeper rings, several per SM, so that no SM
+// waits on the one block it holds and the grid is not cut into a few coarse waves.
 constexpr size_t Q_BYTES = (size_t)(16 + 2) * KS * 2;      // 16 query rows, then the new key and the new value
-constexpr size_t WARP_STAGE_BYTES = (size_t)STAGES * 2 * SLICE * KS * 2;
-constexpr size_t COMBINE_BYTES = (size_t)NWARP * 16 * 2 * 4 + (size_t)NWARP * G * D * 4;
-constexpr size_t PIPE_BYTES = NWARP * WARP_STAGE_BYTES;
-constexpr size_t SMEM_BYTES = Q_BYTES + (PIPE_BYTES > COMBINE_BYTES ? PIPE_BYTES : COMBINE_BYTES);
+template <int NWARP, int STAGES> struct Shape {
+  static constexpr int THREADS = NWARP * 32;
+  static constexpr size_t WARP_STAGE_BYTES = (size_t)STAGES * 2 * SLICE * KS * 2;
+  static constexpr size_t COMBINE_BYTES = (size_t)NWARP * 16 * 2 * 4 + (size_t)NWARP * G * D * 4;
+  static constexpr size_t PIPE_BYTES = NWARP * WARP_STAGE_BYTES;
+  static constexpr size_t SMEM_BYTES = Q_BYTES + (PIPE_BYTES > COMBINE_BYTES ? PIPE_BYTES : COMBINE_BYTES);
+};
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem) {
   unsigned s = (unsigned)__cvta_generic_to_shared(smem);
@@ -133,7 +137,10 @@ struct Params {
   int nKV; int n_splits; float scale; int window; int R; float eps; int has_norm; int write_kv;
 };
 
-__global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
+template <int NWARP, int STAGES>
+__global__ void __launch_bounds__(NWARP * 32) attn_decode_kernel(const Params p) {
+  constexpr int THREADS = Shape<NWARP, STAGES>::THREADS;
+  constexpr size_t WARP_STAGE_BYTES = Shape<NWARP, STAGES>::WARP_STAGE_BYTES;
   extern __shared__ __align__(16) unsigned char smem[];
   bf16* qs = reinterpret_cast<bf16*>(smem);                        // [16][KS], rows >= G zero
   unsigned char* pipe = smem + Q_BYTES;
@@ -409,6 +416,29 @@ __global__ void __launch_bounds__(THREADS) attn_decode_kernel(const Params p) {
   }
   if (tid == 0) p.tickets[n * p.nKV + kvh] = 0;  // ready for the next launch
 }
+template <int NWARP, int STAGES>
+static int launch_shape(const Params& p, int n_rows, int nKV, int n_splits, int pdl, cudaStream_t st) {
+  typedef Shape<NWARP, STAGES> S;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(n_rows, nKV, n_splits);
+  cfg.blockDim = dim3(S::THREADS);
+  static bool attr_set = false;  // per shape; set by the first (eager) launch, outside any stream capture
+  if (S::SMEM_BYTES > 48 * 1024 && !attr_set) {
+    cudaError_t ea = cudaFuncSetAttribute(attn_decode_kernel<NWARP, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM_BYTES);
+    if (ea != cudaSuccess) return (int)ea;
+    attr_set = true;
+  }
+  cfg.dynamicSmemBytes = S::SMEM_BYTES;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, attn_decode_kernel<NWARP, STAGES>, p);
+  if (e != cudaSuccess) return (int)e;
+  return launch_status();
+}
 }  // namespace
 
 DRYFT_API int dryft_attn_decode_head_dim() { return D; }
@@ -418,7 +448,7 @@ DRYFT_API int dryft_attn_decode(const void* qkv, int qkv_stride, const float* wq
                                 const int* tok_slot, const int* tok_pos, void* k_pages, void* v_pages,
                                 const int* page_table, int max_pages, void* out, float* part_o, float* part_ml,
                                 int* tickets, int n_rows, int nKV, int n_splits, float scale, int window, int R, float eps,
-                                int has_norm, int write_kv, int pdl, cudaStream_t st) {
+                                int has_norm, int write_kv, int pdl, int shape, cudaStream_t st) {
   if (n_rows <= 0) return 0;
   if (n_splits < 1 || nKV < 1 || nKV > 65535 || n_splits > 64 || (R & 1) || R > D || R < 0) return DRYFT_ERR_UNSUPPORTED;
   if (n_splits > 1 && (!part_o || !part_ml || !tickets)) return DRYFT_ERR_UNSUPPORTED;
@@ -428,23 +458,21 @@ DRYFT_API int dryft_attn_decode(const void* qkv, int qkv_stride, const float* wq
   p.page_table = page_table; p.max_pages = max_pages; p.out = (bf16*)out; p.part_o = part_o; p.part_ml = part_ml;
   p.tickets = tickets; p.nKV = nKV; p.n_splits = n_splits; p.scale = scale; p.window = window; p.R = R; p.eps = eps;
   p.has_norm = has_norm; p.write_kv = write_kv;
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(n_rows, nKV, n_splits);
-  cfg.blockDim = dim3(THREADS);
-  static bool attr_set = false;  // set by the first (eager) launch, outside any stream capture
-  if (SMEM_BYTES > 48 * 1024 && !attr_set) {
-    cudaError_t ea = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
-    if (ea != cudaSuccess) return (int)ea;
-    attr_set = true;
+  if (shape < 0) {
+    // the widest block shape whose grid is resident at once (no second wave): 8, 4 or 2 warps
+    static int sms = 0;
+    if (sms == 0) {
+      int dev = 0;
+      if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+        sms = 1;
+    }
+    const long long blocks = (long long)n_rows * nKV * n_splits;
+    const long long usable = 227 * 1024;
+    const long long per_sm_8 = usable / (long long)(Shape<8, 2>::SMEM_BYTES + 1024);
+    const long long per_sm_4 = usable / (long long)(Shape<4, 2>::SMEM_BYTES + 1024);
+    shape = blocks <= sms * (per_sm_8 < 1 ? 1 : per_sm_8) ? 0 : (blocks <= sms * per_sm_4 ? 1 : 2);
   }
-  cfg.dynamicSmemBytes = SMEM_BYTES;
-  cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, attn_decode_kernel, p);
-  if (e != cudaSuccess) return (int)e;
-  return launch_status();
+  return shape == 1 ? launch_shape<4, 2>(p, n_rows, nKV, n_splits, pdl, st)
+       : shape == 2 ? launch_shape<2, 2>(p, n_rows, nKV, n_splits, pdl, st)
+                    : launch_shape<8, 2>(p, n_rows, nKV, n_splits, pdl, st);
 }

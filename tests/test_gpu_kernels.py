@@ -374,7 +374,8 @@ def test_attn_rows(dtype, n_heads, n_kv, d, window):
 def test_attn_decode_fused(n_heads, n_kv, d, rot, window):
     """The one-launch decode attention against the plain parts: q/k norm + RoPE of the new token, its
     K/V written into the cache (and nothing else), attention over old keys plus the new one, for
-    every split count; tickets are left at zero."""
+    every split count and every block shape (8, 4, 2 warps, and the launcher's own choice); tickets are
+    left at zero."""
     k = K()
     dtype = torch.bfloat16
     page, theta, eps = 64, 1e4, 1e-5
@@ -406,19 +407,19 @@ def test_attn_decode_fused(n_heads, n_kv, d, rot, window):
         kseq[pos], vseq[pos] = k_r[i], vn[i]
         refs.append(_attn_ref(q_r[i], kseq, vseq, pos, scale, window))
     ref = torch.stack(refs)
-    for splits in (1, 2, 7):
+    for splits, shape in ((1, -1), (2, 0), (7, 1), (1, 2), (3, 2), (1, 1)):
         old = {s: (kv[0][:lens[s]], kv[1][:lens[s]]) for s, kv in seqs.items()}
         # pages for L+1 tokens, only L filled; the rest is a canary the kernel must not touch
         kc, vc, pt = _fill_cache({s: (torch.cat([kv[0], torch.full((1, n_kv, d), 55.0).to(dtype)]),
                                       torch.cat([kv[1], torch.full((1, n_kv, d), 55.0).to(dtype)])) for s, kv in old.items()},
-                                 n_kv, d, page, dtype, n_pages=16, max_pages=5, slots=6, scatter_seed=splits)
+                                 n_kv, d, page, dtype, n_pages=16, max_pages=5, slots=6, scatter_seed=splits + shape)
         kc0, vc0 = kc.clone(), vc.clone()
         out = torch.full((n, n_heads * d), 9.0, device=DEV, dtype=dtype)
         po = torch.empty(n, n_heads, splits, d, device=DEV) if splits > 1 else None
         pm = torch.empty(n, n_heads, splits, 2, device=DEV) if splits > 1 else None
         i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
         k.attn_decode(qkv.to(DEV), wq.to(DEV), wk.to(DEV), inv_freq.to(DEV), i32([r[0] for r in rows]), i32([r[1] for r in rows]),
-                      kc, vc, pt, out, n_heads, n_kv, d, rot, eps, scale, window, splits, po, pm)
+                      kc, vc, pt, out, n_heads, n_kv, d, rot, eps, scale, window, splits, po, pm, shape=shape)
         assert torch.isfinite(out.float()).all()
         torch.testing.assert_close(out.cpu().float(), ref, rtol=2e-2, atol=2e-2)
         changed_k = (kc != kc0).any(dim=-1)
