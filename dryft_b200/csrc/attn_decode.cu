@@ -50,6 +50,7 @@ static_assert(PAGE % SLICE == 0, "page size must be a multiple of 16");
 // while one is used).  Few (row, kv head) pairs: wide blocks, one per SM, so that one sequence's keys
 // are walked by many warps.  Many pairs: narrow blocks with deeper rings, several per SM, so that no SM
 // waits on the one block it holds and the grid is not cut into a few coarse waves.
+constexpr int PT_CACHE = 64;                // page numbers of a block kept in shared memory (more are read from global)
 constexpr size_t Q_BYTES = (size_t)(16 + 2) * KS * 2;      // 16 query rows, then the new key and the new value
 template <int NWARP, int STAGES> struct Shape {
   static constexpr int THREADS = NWARP * 32;
@@ -86,43 +87,78 @@ __device__ __forceinline__ float bfr(float v) { return __bfloat162float(__float2
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
-// One warp: RMSNorm (optional) + RoPE of one head `src` [D] -> dst (bf16).  Same arithmetic as
-// qk_norm_rope_store_kernel.
-__device__ __forceinline__ void norm_rope_head(const bf16* __restrict__ src, const float* __restrict__ w,
-                                               const float* __restrict__ inv_freq, int pos, int R, float eps, int has_norm,
-                                               bf16* dst, bf16* dst2, int lane) {
+// Rotary constants of one token for a lane: pairs j = lane + 32 * jj.  They depend on the position only.
+constexpr int MAXJ = (D / 2 + 31) / 32;
+struct RopeConsts {
+  float cs[MAXJ], sn[MAXJ];            // cos / sin, rounded to bfloat16
+  float wq_a[MAXJ], wq_b[MAXJ];        // q norm weight at j and j + R/2
+  float wk_a[MAXJ], wk_b[MAXJ];        // k norm weight
+};
+__device__ __forceinline__ void rope_consts(RopeConsts& c, const float* __restrict__ wq, const float* __restrict__ wk,
+                                            const float* __restrict__ inv_freq, int pos, int R, int has_norm, int lane) {
+  const int half = R >> 1;
+#pragma unroll
+  for (int jj = 0; jj < MAXJ; ++jj) {
+    const int j = lane + 32 * jj;
+    c.cs[jj] = 1.f; c.sn[jj] = 0.f;
+    c.wq_a[jj] = c.wq_b[jj] = c.wk_a[jj] = c.wk_b[jj] = 1.f;
+    if (j < half) {
+      float sn, cs;
+      sincosf((float)pos * inv_freq[j], &sn, &cs);
+      c.cs[jj] = bfr(cs);
+      c.sn[jj] = bfr(sn);
+      if (has_norm) { c.wq_a[jj] = wq[j]; c.wq_b[jj] = wq[j + half]; c.wk_a[jj] = wk[j]; c.wk_b[jj] = wk[j + half]; }
+    }
+  }
+}
+// One warp: RMSNorm (optional) + RoPE of one head `src` [D] -> dst (bf16), with the token's constants
+// already in registers: one read of the head, one reduction, one write.  Same arithmetic as
+// qk_norm_rope_store_kernel.  `w` is only read for dims beyond the rotary part.
+__device__ __forceinline__ void norm_rope_head(const bf16* __restrict__ src, const float* __restrict__ w, const RopeConsts& c,
+                                               bool is_q, int R, float eps, int has_norm, bf16* dst, bf16* dst2, int lane) {
+  const int half = R >> 1;
+  float a[MAXJ], b[MAXJ];
+  float ss = 0.f;
+#pragma unroll
+  for (int jj = 0; jj < MAXJ; ++jj) {
+    const int j = lane + 32 * jj;
+    a[jj] = b[jj] = 0.f;
+    if (j < half) {
+      a[jj] = __bfloat162float(src[j]);
+      b[jj] = __bfloat162float(src[j + half]);
+      ss += a[jj] * a[jj] + b[jj] * b[jj];
+    }
+  }
   float inv = 1.f;
   if (has_norm) {
-    float ss = 0.f;
-    for (int i = lane; i < D; i += 32) {
+    for (int i = R + lane; i < D; i += 32) {
       const float v = __bfloat162float(src[i]);
       ss += v * v;
     }
     ss = warp_sum(ss);
     inv = rsqrtf(ss / (float)D + eps);
   }
-  const int half = R >> 1;
-  for (int j = lane; j < half; j += 32) {
-    float a = __bfloat162float(src[j]), b = __bfloat162float(src[j + half]);
-    if (has_norm) {
-      a = bfr(bfr(a * inv) * w[j]);
-      b = bfr(bfr(b * inv) * w[j + half]);
+#pragma unroll
+  for (int jj = 0; jj < MAXJ; ++jj) {
+    const int j = lane + 32 * jj;
+    if (j < half) {
+      float x = a[jj], y = b[jj];
+      if (has_norm) {
+        x = bfr(bfr(x * inv) * (is_q ? c.wq_a[jj] : c.wk_a[jj]));
+        y = bfr(bfr(y * inv) * (is_q ? c.wq_b[jj] : c.wk_b[jj]));
+      }
+      const bf16 o1 = __float2bfloat16_rn(__fadd_rn(bfr(__fmul_rn(x, c.cs[jj])), -bfr(__fmul_rn(y, c.sn[jj]))));
+      const bf16 o2 = __float2bfloat16_rn(__fadd_rn(bfr(__fmul_rn(y, c.cs[jj])), bfr(__fmul_rn(x, c.sn[jj]))));
+      dst[j] = o1;
+      dst[j + half] = o2;
+      if (dst2) { dst2[j] = o1; dst2[j + half] = o2; }
     }
-    float sn, cs;
-    sincosf((float)pos * inv_freq[j], &sn, &cs);
-    cs = bfr(cs);
-    sn = bfr(sn);
-    const bf16 o1 = __float2bfloat16_rn(__fadd_rn(bfr(__fmul_rn(a, cs)), -bfr(__fmul_rn(b, sn))));
-    const bf16 o2 = __float2bfloat16_rn(__fadd_rn(bfr(__fmul_rn(b, cs)), bfr(__fmul_rn(a, sn))));
-    dst[j] = o1;
-    dst[j + half] = o2;
-    if (dst2) { dst2[j] = o1; dst2[j + half] = o2; }
   }
   for (int i = R + lane; i < D; i += 32) {
-    float a = __bfloat162float(src[i]);
-    if (has_norm) a = bfr(bfr(a * inv) * w[i]);
-    dst[i] = __float2bfloat16_rn(a);
-    if (dst2) dst2[i] = __float2bfloat16_rn(a);
+    float x = __bfloat162float(src[i]);
+    if (has_norm) x = bfr(bfr(x * inv) * w[i]);
+    dst[i] = __float2bfloat16_rn(x);
+    if (dst2) dst2[i] = __float2bfloat16_rn(x);
   }
 }
 
@@ -151,15 +187,13 @@ __global__ void __launch_bounds__(NWARP * 32) attn_decode_kernel(const Params p)
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
 
+  DRYFT_TRACE_NOW(tr0);
   pdl_launch_dependents();
-  pdl_wait();  // the projection that made qkv, and this step's token metadata, are complete
-
+  // What does not depend on the projection before this launch is done before waiting for it: the step's
+  // token metadata and page table (complete before the step's first programmatic launch; the block's
+  // page numbers go to shared memory), the token's rotary constants and norm weights, and, in a layer
+  // that writes its own cache, the warps' first requests for keys and values of earlier tokens.
   const int slot = p.tok_slot[n];
-  if (slot < 0) {  // padding row: defined zeros (written by split 0), no cache access, no ticket
-    if (split == 0)
-      for (int i = tid; i < G * D; i += THREADS) p.out[(size_t)n * nH * D + (size_t)kvh * G * D + i] = __float2bfloat16_rn(0.f);
-    return;
-  }
   const int pos = p.tok_pos[n];
   const int kv_hi = pos + 1;
   const int kv_lo = p.window > 0 ? max(0, kv_hi - p.window) : 0;
@@ -168,9 +202,14 @@ __global__ void __launch_bounds__(NWARP * 32) attn_decode_kernel(const Params p)
   const int per_split = (n_pages + p.n_splits - 1) / p.n_splits;
   const int pg_begin = first_page + split * per_split;
   const int pg_end = min(pg_begin + per_split, last_page + 1);
-  const int* pt = p.page_table + (size_t)slot * p.max_pages;
-  const bf16* row = p.qkv + (size_t)n * p.qkv_stride;
-
+  const int* pt = p.page_table + (size_t)(slot < 0 ? 0 : slot) * p.max_pages;
+  __shared__ int pt_s[PT_CACHE];
+  if (slot >= 0)
+    for (int i = tid; i < min(pg_end - pg_begin, PT_CACHE); i += THREADS) pt_s[i] = pt[pg_begin + i];
+  RopeConsts rc;
+  if (slot >= 0) rope_consts(rc, p.wq, p.wk, p.inv_freq, pos, p.R, p.has_norm, lane);
+  __syncthreads();
+  auto page_of = [&](int pg) { return pg - pg_begin < PT_CACHE ? pt_s[pg - pg_begin] : pt[pg]; };
   // ---- each warp's first slices are requested before anything else is computed ----
   bf16* stage = reinterpret_cast<bf16*>(pipe + (size_t)warp * WARP_STAGE_BYTES);  // [STAGES][K|V][SLICE][KS]
   // slices of this block, in key order: slice index sl covers keys sl*16 .. sl*16+15
@@ -185,7 +224,7 @@ __global__ void __launch_bounds__(NWARP * 32) attn_decode_kernel(const Params p)
   auto request = [&](int sl, int st) {
     if (sl < sl_end) {
       const int pg = sl / SPP;
-      const size_t base = (((size_t)pt[pg] * p.nKV + kvh) * PAGE + (size_t)(sl % SPP) * SLICE) * D;
+      const size_t base = (((size_t)page_of(pg) * p.nKV + kvh) * PAGE + (size_t)(sl % SPP) * SLICE) * D;
       const bf16* ksrc = p.k_pages + base + (size_t)lr * D + lc * 8;
       const bf16* vsrc = p.v_pages + base + (size_t)lr * D + lc * 8;
       bf16* kd = stage + (size_t)st * 2 * SLICE * KS + lr * KS + lc * 8;
@@ -202,8 +241,27 @@ __global__ void __launch_bounds__(NWARP * 32) attn_decode_kernel(const Params p)
     }
     cp_async_commit();
   };
+  // a layer that reads another layer's cache must see that layer's write of this step's token first
+  const bool early = slot >= 0 && p.write_kv;
+  if (early) {
 #pragma unroll
-  for (int i = 0; i < STAGES - 1; ++i) request(sl_begin + warp + i * NWARP, i);
+    for (int i = 0; i < STAGES - 1; ++i) request(sl_begin + warp + i * NWARP, i);
+  }
+
+  pdl_wait();  // the projection that made qkv is complete
+
+  DRYFT_TRACE_NOW(tr1);
+  if (slot < 0) {  // padding row: defined zeros (written by split 0), no cache access, no ticket
+    if (split == 0)
+      for (int i = tid; i < G * D; i += THREADS) p.out[(size_t)n * nH * D + (size_t)kvh * G * D + i] = __float2bfloat16_rn(0.f);
+    return;
+  }
+  const bf16* row = p.qkv + (size_t)n * p.qkv_stride;
+
+  if (!early) {
+#pragma unroll
+    for (int i = 0; i < STAGES - 1; ++i) request(sl_begin + warp + i * NWARP, i);
+  }
 
   // ---- the row's queries; and, in the block that owns the last page, the new key and value ----
   bf16* new_k = qs + 16 * KS;
@@ -214,11 +272,11 @@ __global__ void __launch_bounds__(NWARP * 32) attn_decode_kernel(const Params p)
   const int n_items = G + (owns_new ? 2 : 0);
   for (int item = warp; item < n_items; item += NWARP) {
     if (item < G) {
-      norm_rope_head(row + (size_t)(kvh * G + item) * D, p.wq, p.inv_freq, pos, p.R, p.eps, p.has_norm, qs + item * KS, nullptr, lane);
+      norm_rope_head(row + (size_t)(kvh * G + item) * D, p.wq, rc, true, p.R, p.eps, p.has_norm, qs + item * KS, nullptr, lane);
     } else {
-      const size_t off = (((size_t)pt[last_page] * p.nKV + kvh) * PAGE + (pos % PAGE)) * D;
+      const size_t off = (((size_t)page_of(last_page) * p.nKV + kvh) * PAGE + (pos % PAGE)) * D;
       if (item == G) {
-        norm_rope_head(row + (size_t)(nH + kvh) * D, p.wk, p.inv_freq, pos, p.R, p.eps, p.has_norm, p.k_pages + off, new_k, lane);
+        norm_rope_head(row + (size_t)(nH + kvh) * D, p.wk, rc, false, p.R, p.eps, p.has_norm, p.k_pages + off, new_k, lane);
       } else {
         const bf16* vsrc = row + (size_t)(nH + p.nKV + kvh) * D;
         for (int i = lane; i < D; i += 32) {
@@ -230,6 +288,7 @@ __global__ void __launch_bounds__(NWARP * 32) attn_decode_kernel(const Params p)
     }
   }
   __syncthreads();  // queries (and the new key and value) are in shared memory
+  DRYFT_TRACE_NOW(tr2);
 
   // ---- each warp walks its own 16-key slices of the block's pages ----
   float o_acc[DT][4];
@@ -369,7 +428,10 @@ __global__ void __launch_bounds__(NWARP * 32) attn_decode_kernel(const Params p)
       if (d == 0) { p.part_ml[(pidx * G + h) * 2] = mx; p.part_ml[(pidx * G + h) * 2 + 1] = den; }
     }
   }
-  if (p.n_splits == 1) return;
+  if (p.n_splits == 1) {
+    DRYFT_TRACE_PUT(1u, tr0, tr1, tr2);
+    return;
+  }
 
   // ---- the block that draws the last ticket combines all splits, in split order ----
   __threadfence();
@@ -443,6 +505,7 @@ static int launch_shape(const Params& p, int n_rows, int nKV, int n_splits, int 
 
 DRYFT_API int dryft_attn_decode_head_dim() { return D; }
 DRYFT_API int dryft_attn_decode_group() { return G; }
+DRYFT_TRACE_EXPORT(dryft_attn_decode_trace)
 
 DRYFT_API int dryft_attn_decode(const void* qkv, int qkv_stride, const float* wq, const float* wk, const float* inv_freq,
                                 const int* tok_slot, const int* tok_pos, void* k_pages, void* v_pages,

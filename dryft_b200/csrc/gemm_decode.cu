@@ -76,6 +76,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
   const int n_tiles = (N + TILE_N - 1) / TILE_N;
   const int k_warp = warp * SPW * 32 + t * 8;   // this thread's first k
 
+  DRYFT_TRACE_NOW(tr0);
   pdl_launch_dependents();
 
   uint4 wa[CHUNK], wb[CHUNK];
@@ -106,11 +107,36 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
     request(w0, w1, 0);  // weights depend on no earlier launch
   }
 
+  float* nw_s = reinterpret_cast<float*>(a_res + (size_t)MP * KA);   // the norm's weight (K floats)
+  if (NORM) {
+    // the norm's weight depends on no earlier launch either: into shared memory before the wait
+    for (int i = tid; i < K / 4; i += THREADS)
+      reinterpret_cast<float4*>(nw_s)[i] = __ldg(reinterpret_cast<const float4*>(norm_w) + i);
+  }
+
   pdl_wait();  // from here on, what earlier launches wrote (activations, sums of squares) is visible
+  DRYFT_TRACE_NOW(tr1);
 
   if (NORM) {
     // inv[m] = rsqrt(mean(x[m]^2) + eps): warp m adds the blocks of sums of squares in a fixed order;
-    // then the normalised rows a[m,k] = T(T(x[m,k] * inv[m]) * w[k]) go to shared memory once per block
+    // then the normalised rows a[m,k] = T(T(x[m,k] * inv[m]) * w[k]) go to shared memory once per block.
+    // The activations are requested together with the sums of squares, a batch of loads per thread
+    // at once, so that the whole prologue is one or two trips to memory.
+    constexpr int CHUNKS = K / 8;
+    constexpr int ITEMS = MP * CHUNKS;            // 16-byte pieces of the activations; ITEMS % THREADS == 0
+    constexpr int PER = ITEMS / THREADS;          // pieces per thread
+    constexpr int BATCH = PER <= 5 ? PER : 5;     // pieces a thread requests together (registers also hold the first weights)
+    static_assert(ITEMS % THREADS == 0, "K is a multiple of 256");
+    uint4 raw[BATCH];
+    auto fetch = [&](int first) {
+#pragma unroll
+      for (int u = 0; u < BATCH; ++u) {
+        const int i = tid + (first + u) * THREADS;
+        const int m = i / CHUNKS, c = i - m * CHUNKS;
+        raw[u] = (first + u < PER && m < M) ? __ldg(reinterpret_cast<const uint4*>(A + (size_t)m * lda + c * 8)) : zero;
+      }
+    };
+    fetch(0);
     for (int m = warp; m < MP; m += WARPS) {
       float s = 0.f;
       if (m < M)
@@ -118,25 +144,29 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
       s = warp_sum(s);
       if (lane == 0) inv_s[m] = rsqrtf(s / (float)K + eps);
     }
-    __syncthreads();
-    constexpr int CHUNKS = K / 8;
-#pragma unroll 4
-    for (int i = tid; i < MP * CHUNKS; i += THREADS) {
-      const int m = i / CHUNKS, c = i - m * CHUNKS;
-      uint4 out = zero;
-      if (m < M) {
-        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(A + (size_t)m * lda + c * 8));
-        const float4 wv0 = __ldg(reinterpret_cast<const float4*>(norm_w + c * 8));
-        const float4 wv1 = __ldg(reinterpret_cast<const float4*>(norm_w + c * 8 + 4));
-        const float wv[8] = {wv0.x, wv0.y, wv0.z, wv0.w, wv1.x, wv1.y, wv1.z, wv1.w};
-        const bf16* e = reinterpret_cast<const bf16*>(&raw);
-        const float inv = inv_s[m];
-        __align__(16) bf16 o[8];
+    __syncthreads();   // inv_s and the norm's weight are in shared memory
+#pragma unroll 1
+    for (int first = 0; first < PER; first += BATCH) {
+      if (first > 0) fetch(first);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16_rn(bfr(__bfloat162float(e[j]) * inv) * wv[j]);
-        out = *reinterpret_cast<const uint4*>(o);
+      for (int u = 0; u < BATCH; ++u) {
+        if (first + u >= PER) break;
+        const int i = tid + (first + u) * THREADS;
+        const int m = i / CHUNKS, c = i - m * CHUNKS;
+        uint4 out = zero;
+        if (m < M) {
+          const float4 wv0 = *reinterpret_cast<const float4*>(nw_s + c * 8);
+          const float4 wv1 = *reinterpret_cast<const float4*>(nw_s + c * 8 + 4);
+          const float wv[8] = {wv0.x, wv0.y, wv0.z, wv0.w, wv1.x, wv1.y, wv1.z, wv1.w};
+          const bf16* e = reinterpret_cast<const bf16*>(&raw[u]);
+          const float inv = inv_s[m];
+          __align__(16) bf16 o[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16_rn(bfr(__bfloat162float(e[j]) * inv) * wv[j]);
+          out = *reinterpret_cast<const uint4*>(o);
+        }
+        *reinterpret_cast<uint4*>(a_res + (size_t)m * KA + c * 8) = out;
       }
-      *reinterpret_cast<uint4*>(a_res + (size_t)m * KA + c * 8) = out;
     }
     __syncthreads();
   }
@@ -144,6 +174,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
   const bf16* a_frag = NORM ? a_res + (size_t)g * KA + k_warp : A + (size_t)g * lda + k_warp;
   const size_t a_mb = NORM ? (size_t)8 * KA : (size_t)8 * lda;
 
+  DRYFT_TRACE_NOW(tr2);
   int buf = 0;
   for (; tile < n_tiles; tile += gridDim.x) {
     float acc[MB][4];
@@ -231,6 +262,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
       }
     }
   }
+  DRYFT_TRACE_PUT((unsigned)(K * 16 + MODE * 2 + (NORM ? 1 : 0)), tr0, tr1, tr2);
 }
 
 template <int MB, int MODE, bool NORM>
@@ -238,7 +270,7 @@ int launch3(const void* A, int lda, const void* W, void* C, int ldc, int M, int 
             const float* ss_in, int ss_parts, float eps, float* ss_out, int pdl, cudaStream_t st) {
   constexpr int MP = 8 * MB;
   size_t smem = (size_t)2 * WARPS * ROWS * (MP + 1) * 4 + SS_STRIDE * 4;
-  if (NORM) smem += (size_t)MP * KA * 2;
+  if (NORM) smem += (size_t)MP * KA * 2 + (size_t)K * 4;
   if (smem > 110 * 1024) return DRYFT_ERR_UNSUPPORTED;
   static size_t attr_bytes = 48 * 1024;  // per instantiation; raised by an eager launch before any capture
   if (smem > attr_bytes) {
@@ -246,8 +278,9 @@ int launch3(const void* A, int lda, const void* W, void* C, int ldc, int M, int 
     if (e != cudaSuccess) return (int)e;
     attr_bytes = smem;
   }
-  // persistent blocks: two per SM at most, each taking every grid-th tile; the grid is chosen so
-  // that the tiles divide as evenly as they can
+  // Persistent blocks, two per SM, each taking every grid-th tile.  What an SM can pull from memory is
+  // bounded by the requests its blocks keep in flight, so the tiles are spread over all SMs as evenly as
+  // they go: with the usual placement (block b beside block b + SMs) the SMs' totals differ by one tile.
   static int max_blocks = 0;
   if (max_blocks == 0) {
     int dev = 0, sms = 0;
@@ -256,8 +289,7 @@ int launch3(const void* A, int lda, const void* W, void* C, int ldc, int M, int 
     max_blocks = 2 * (sms > 0 ? sms : 148);
   }
   const int n_tiles = MODE == SILU ? (N + 7) / 8 : (N + ROWS - 1) / ROWS;
-  const int rounds = (n_tiles + max_blocks - 1) / max_blocks;
-  const unsigned blocks = (unsigned)((n_tiles + rounds - 1) / rounds);
+  const unsigned blocks = (unsigned)(n_tiles < max_blocks ? n_tiles : max_blocks);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(blocks);
   cfg.blockDim = dim3(THREADS);
@@ -293,6 +325,7 @@ int launch1(int mode, bool norm, const void* A, int lda, const void* W, void* C,
 }  // namespace
 
 DRYFT_API int dryft_gemm_decode_k() { return K; }
+DRYFT_TRACE_EXPORT(dryft_gemm_decode_trace)
 
 // Same contract as dryft_gemm_small_m (csrc/gemm_small_m.cu) for this library's K.  A residual product
 // of N outputs leaves ceil(N/16) blocks of sums of squares in ss_out.
