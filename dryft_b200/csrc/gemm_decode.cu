@@ -107,11 +107,14 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
     request(w0, w1, 0);  // weights depend on no earlier launch
   }
 
-  float* nw_s = reinterpret_cast<float*>(a_res + (size_t)MP * KA);   // the norm's weight (K floats)
+  bf16* nw_s = a_res + (size_t)MP * KA;   // the norm's weight as bfloat16 (its values are bfloat16 values held in 32-bit)
   if (NORM) {
     // the norm's weight depends on no earlier launch either: into shared memory before the wait
-    for (int i = tid; i < K / 4; i += THREADS)
-      reinterpret_cast<float4*>(nw_s)[i] = __ldg(reinterpret_cast<const float4*>(norm_w) + i);
+    for (int i = tid; i < K / 4; i += THREADS) {
+      const float4 v = __ldg(reinterpret_cast<const float4*>(norm_w) + i);
+      reinterpret_cast<__nv_bfloat162*>(nw_s)[2 * i] = __floats2bfloat162_rn(v.x, v.y);
+      reinterpret_cast<__nv_bfloat162*>(nw_s)[2 * i + 1] = __floats2bfloat162_rn(v.z, v.w);
+    }
   }
 
   pdl_wait();  // from here on, what earlier launches wrote (activations, sums of squares) is visible
@@ -155,14 +158,18 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
         const int m = i / CHUNKS, c = i - m * CHUNKS;
         uint4 out = zero;
         if (m < M) {
-          const float4 wv0 = *reinterpret_cast<const float4*>(nw_s + c * 8);
-          const float4 wv1 = *reinterpret_cast<const float4*>(nw_s + c * 8 + 4);
-          const float wv[8] = {wv0.x, wv0.y, wv0.z, wv0.w, wv1.x, wv1.y, wv1.z, wv1.w};
-          const bf16* e = reinterpret_cast<const bf16*>(&raw[u]);
+          // two elements at a time: x * inv in 32-bit, rounded to a bfloat16 pair, times the weight pair
+          // (a bfloat16 product rounded once: the same value as the 32-bit product rounded)
+          const uint4 wraw = *reinterpret_cast<const uint4*>(nw_s + c * 8);
+          const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wraw);
+          const __nv_bfloat162* e = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
           const float inv = inv_s[m];
-          __align__(16) bf16 o[8];
+          __align__(16) __nv_bfloat162 o[4];
 #pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] = __float2bfloat16_rn(bfr(__bfloat162float(e[j]) * inv) * wv[j]);
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(e[j]);
+            o[j] = __hmul2(__floats2bfloat162_rn(f.x * inv, f.y * inv), wp[j]);
+          }
           out = *reinterpret_cast<const uint4*>(o);
         }
         *reinterpret_cast<uint4*>(a_res + (size_t)m * KA + c * 8) = out;
@@ -270,7 +277,7 @@ int launch3(const void* A, int lda, const void* W, void* C, int ldc, int M, int 
             const float* ss_in, int ss_parts, float eps, float* ss_out, int pdl, cudaStream_t st) {
   constexpr int MP = 8 * MB;
   size_t smem = (size_t)2 * WARPS * ROWS * (MP + 1) * 4 + SS_STRIDE * 4;
-  if (NORM) smem += (size_t)MP * KA * 2 + (size_t)K * 4;
+  if (NORM) smem += (size_t)MP * KA * 2 + (size_t)K * 2;
   if (smem > 110 * 1024) return DRYFT_ERR_UNSUPPORTED;
   static size_t attr_bytes = 48 * 1024;  // per instantiation; raised by an eager launch before any capture
   if (smem > attr_bytes) {

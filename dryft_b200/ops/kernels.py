@@ -112,6 +112,23 @@ def gemm_decode_lib(k: int) -> ctypes.CDLL:
         return lib
 
 
+_gemm_stream: Optional[ctypes.CDLL] = None
+
+
+def gemm_stream_lib() -> ctypes.CDLL:
+    """The weight-streaming decode product on tcgen05 / TMEM / TMA with cluster split-K."""
+    global _gemm_stream
+    with _lock:
+        if _gemm_stream is None:
+            lib = _load(build.build_library("gemm_stream", ("gemm_stream.cu",)))
+            lib.dryft_gemm_stream.argtypes = [_p, _i, _p, _p, _i, _i, _i, _i, _i, _p, _p, _i, _f, _p, _i, _p, _p]
+            lib.dryft_gemm_stream.restype = _i
+            lib.dryft_gemm_stream_ss_parts.argtypes = [_i, _i]
+            lib.dryft_gemm_stream_ss_parts.restype = _i
+            _gemm_stream = lib
+        return _gemm_stream
+
+
 _gemm_tc: Optional[ctypes.CDLL] = None
 
 
@@ -605,6 +622,51 @@ def gemm_small_m(a, w, out, *, mode: str = "store", norm_w=None, ss_in=None, ss_
     _ok(core().dryft_gemm_small_m(_ptr(a), k, _ptr(w), _ptr(out), n, code, m, n, k, _ptr(norm_w), _ptr(ss_in),
                                   int(ss_parts), float(eps), _ptr(ss_out), int(pdl), _stream()),
         f"gemm_small_m (M={m}, N={n}, K={k}, mode={mode})")
+
+
+STREAM_M_LIMIT = 64
+
+
+def gemm_stream_supported(m: int, k: int) -> bool:
+    return 0 < m <= STREAM_M_LIMIT and k > 0 and k % 64 == 0
+
+
+def gemm_stream_ss_parts(n_out: int, k_in: int) -> int:
+    """Blocks of sums of squares that ``gemm_stream(mode="residual")`` leaves in ``ss_out``."""
+    return int(gemm_stream_lib().dryft_gemm_stream_ss_parts(int(n_out), int(k_in)))
+
+
+def gemm_stream(a, w, out, *, mode: str = "store", norm_w=None, ss_in=None, ss_parts: int = 0, eps: float = 0.0,
+                ss_out=None, pdl: bool = False) -> None:
+    """``gemm_small_m``'s contract for up to 64 rows, on tcgen05 with the weights streamed by TMA through
+    shared-memory rings and K split over a thread-block cluster.  ``ss_out`` must hold
+    ``gemm_stream_ss_parts(N, K)`` blocks of 64 floats."""
+    m, k = a.shape
+    _need(a, "a", torch.bfloat16)
+    if not gemm_stream_supported(m, k):
+        raise KernelError(f"gemm_stream takes 1..{STREAM_M_LIMIT} rows and inner sizes that are multiples of 64, got M={m}, K={k}")
+    code = {"store": 1 if out.dtype == torch.float32 else 0, "residual": 2, "silu": 3}.get(mode)
+    if code is None:
+        raise KernelError(f"gemm_stream: unknown mode {mode!r}")
+    rows = w.shape[0]
+    n = rows // 2 if mode == "silu" else rows
+    _need(w, "w", torch.bfloat16, (2 * n if mode == "silu" else n, k))
+    _need(out, "out", torch.float32 if code == 1 else torch.bfloat16, (m, n))
+    if norm_w is not None:
+        _need(norm_w, "norm weight", torch.float32, (k,))
+        _need(ss_in, "ss_in", torch.float32)
+        if ss_parts <= 0 or ss_in.numel() < ss_parts * SS_STRIDE:
+            raise KernelError("gemm_stream: ss_in does not hold ss_parts blocks")
+    if ss_out is not None:
+        if mode != "residual":
+            raise KernelError("gemm_stream: ss_out belongs to mode='residual'")
+        _need(ss_out, "ss_out", torch.float32)
+        if ss_out.numel() < gemm_stream_ss_parts(n, k) * SS_STRIDE:
+            raise KernelError("gemm_stream: ss_out too small")
+    _ok(gemm_stream_lib().dryft_gemm_stream(_ptr(a), k, _ptr(w), _ptr(out), n, code, m, n, k, _ptr(norm_w), _ptr(ss_in),
+                                            int(ss_parts), float(eps), _ptr(ss_out), int(pdl), _ptr(error_flag(a.device)),
+                                            _stream()),
+        f"gemm_stream (M={m}, N={n}, K={k}, mode={mode})")
 
 
 def row_sumsq(x, ss) -> None:

@@ -200,6 +200,63 @@ def test_gemm_small_m_fused_norm_residual_silu(m, n, k_):
     torch.testing.assert_close(act.cpu().float(), want.float(), rtol=3e-2, atol=3e-2)
 
 
+@pytest.mark.parametrize("m", [1, 8, 13, 40, 64])
+@pytest.mark.parametrize("n,k_", [(2560, 2560), (6144, 2560), (2560, 9728), (1000, 192), (200, 128), (19456, 256)])
+def test_gemm_stream(m, n, k_):
+    """The weight-streaming decode product (tcgen05, TMA rings, cluster split-K) against the plain parts, in
+    every form: store (bfloat16 and 32-bit), norm prologue from sums of squares, residual add leaving new
+    sums of squares that a second product normalises from, SiLU*mul; 1..64 rows, output counts that are no
+    multiple of the 128-row tile, every cluster size."""
+    k = K()
+    bf = torch.bfloat16
+    eps = 1e-5
+    x = (torch.randn(m, k_, device=DEV) * 2).to(bf)
+    nw = (1 + 0.1 * torch.randn(k_, device=DEV)).to(bf).float()
+    w = (torch.randn(n, k_, device=DEV) / math.sqrt(k_)).to(bf)
+    # plain store, both output types; a row's result does not depend on the other rows
+    out = torch.empty(m, n, device=DEV, dtype=bf)
+    k.gemm_stream(x, w, out)
+    ref = x.cpu().double() @ w.cpu().double().T
+    torch.testing.assert_close(out.cpu().double(), ref, rtol=2e-2, atol=2e-2)
+    out32 = torch.empty(m, n, device=DEV, dtype=torch.float32)
+    k.gemm_stream(x, w, out32)
+    torch.testing.assert_close(out32.cpu().double(), ref, rtol=1e-3, atol=1e-3)
+    one = torch.empty(1, n, device=DEV, dtype=torch.float32)
+    k.gemm_stream(x[m - 1:].contiguous(), w, one)
+    assert torch.equal(one[0], out32[m - 1])
+    # norm prologue
+    ss = torch.zeros(64, device=DEV)
+    k.row_sumsq(x, ss)
+    h_ref = P.rmsnorm(x.cpu(), nw.cpu(), eps)
+    k.gemm_stream(x, w, out, norm_w=nw, ss_in=ss, ss_parts=1, eps=eps)
+    torch.testing.assert_close(out.cpu().double(), h_ref.double() @ w.cpu().double().T, rtol=2e-2, atol=2e-2)
+    # residual epilogue with sums of squares, chained into a second normalised product
+    res = torch.randn(m, n, device=DEV).to(bf)
+    res0 = res.clone()
+    parts = k.gemm_stream_ss_parts(n, k_)
+    ss_out = torch.full((parts * 64,), -1.0, device=DEV)
+    k.gemm_stream(x, w, res, mode="residual", ss_out=ss_out)
+    want = P.residual_add(res0.cpu(), P.matmul_nt(x.cpu(), w.cpu(), bf))
+    torch.testing.assert_close(res.cpu().float(), want.float(), rtol=2e-2, atol=2e-2)
+    got_ss = ss_out.view(parts, 64)[:, :m].sum(0).cpu()
+    torch.testing.assert_close(got_ss, res.float().pow(2).sum(-1).cpu(), rtol=1e-4, atol=1e-4)
+    if n % 64 == 0:
+        w2 = (torch.randn(48, n, device=DEV) / math.sqrt(n)).to(bf)
+        nw2 = (1 + 0.1 * torch.randn(n, device=DEV)).to(bf).float()
+        out2 = torch.empty(m, 48, device=DEV, dtype=torch.float32)
+        k.gemm_stream(res, w2, out2, norm_w=nw2, ss_in=ss_out, ss_parts=parts, eps=eps)
+        ref2 = P.rmsnorm(res.cpu(), nw2.cpu(), eps).double() @ w2.cpu().double().T
+        torch.testing.assert_close(out2.cpu().double(), ref2, rtol=2e-2, atol=2e-2)
+    # SiLU*mul over gate rows then up rows
+    inter = n // 2
+    act = torch.empty(m, inter, device=DEV, dtype=bf)
+    k.gemm_stream(x, w[: 2 * inter], act, mode="silu")
+    gu = P.matmul_nt(x.cpu(), w[: 2 * inter].cpu(), bf)
+    torch.testing.assert_close(act.cpu().float(), P.silu_mul(gu[:, :inter], gu[:, inter:]).float(), rtol=3e-2, atol=3e-2)
+    torch.cuda.synchronize()
+    k.check_error_flags()
+
+
 @pytest.mark.parametrize("m,n,k_", [(128, 256, 64), (100, 300, 128), (333, 2560, 512), (2048, 1024, 2560)])
 @pytest.mark.parametrize("mode", ["store", "residual", "silu"])
 def test_gemm_tc(m, n, k_, mode):
