@@ -45,7 +45,7 @@ class EngineOptions:
     page_size: int = 64
     cuda_graphs: bool = True
     device: str = "cuda:0"
-    small_m_max: int = 16
+    small_m_max: int = 8                   # rows up to which decode products stream weights themselves (cuBLAS above)
     fuse_decode: bool = True               # fold norms, adds and SiLU*mul into the decode products
     pdl: bool = True                       # programmatic dependent launch between the decode products
     tcgen05: bool = True                   # prefill attention on tcgen05 / TMEM / TMA where the head size allows

@@ -49,7 +49,7 @@ class Runtime:
     device: torch.device
     page_size: int = 64
     sm_count: int = 148
-    small_m_max: int = 16        # decode rows up to which the weight-streaming product is used
+    small_m_max: int = 8         # decode rows up to which the weight-streaming product is used (9..16 rows run, but slower than the library)
     ffn_chunk_rows: int = 16384  # rows of the feed-forward processed at once (bounds [rows, 2I])
     fuse_decode: bool = True     # few rows: fold norms, residual adds and SiLU*mul into the products
     pdl: bool = True             # launch the fused decode products as programmatic dependents
