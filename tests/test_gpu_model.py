@@ -547,3 +547,141 @@ def test_layer_reading_another_layers_cache():
             del eng
     finally:
         unregister_architecture("SharedKVForCausalLM")
+
+
+@pytest.mark.gpu
+def test_toy_routed_ffn_and_toy_position_encoding_register_build_and_step():
+    """Two more parts defined here and registered without a change to the library: a feed-forward that
+    routes every token to one of three small experts (router logits in 32-bit, first index on ties) and a
+    rotary position encoding with interpolated positions (angles = pos / factor * inv_freq).  A new
+    architecture uses them in different layers (the first layer keeps the stock parts); whole prompts,
+    token by token, two sequences in a batch, and a plain evaluation written out here must agree."""
+    from dryft_b200.config import register_architecture, unregister_architecture
+    from dryft_b200.config.spec import LayerSpec, ModelSpec, PartSpec, RunStep
+    from dryft_b200.engine.api import Engine
+    from dryft_b200.parts import FFNS, POSITIONS, TensorInfo, register_ffn, register_position
+    from dryft_b200.parts.linear import linear
+
+    n_exp, inter = 3, 40
+
+    class RoutedFFN:
+        @staticmethod
+        def tensors(params, prefix):
+            h = params["hidden_size"]
+            t = {prefix + "router.weight": TensorInfo((n_exp, h), "matrix")}
+            for e in range(n_exp):
+                t[prefix + f"experts.{e}.up.weight"] = TensorInfo((inter, h), "matrix")
+                t[prefix + f"experts.{e}.down.weight"] = TensorInfo((h, inter), "matrix")
+            return t
+
+        def __init__(self, params, prefix, weights, rt):
+            self.rt = rt
+            self.router = weights.load(prefix + "router.weight", "matrix")
+            self.up = [weights.load(prefix + f"experts.{e}.up.weight", "matrix") for e in range(n_exp)]
+            self.down = [weights.load(prefix + f"experts.{e}.down.weight", "matrix") for e in range(n_exp)]
+
+        def forward(self, h, ctx):
+            logits = h.float() @ self.router.float().T          # router logits in 32-bit
+            choice = logits.argmax(dim=-1)                       # first index on ties
+            out = torch.zeros_like(h)
+            for e in range(n_exp):
+                rows = (choice == e).nonzero(as_tuple=True)[0]
+                if rows.numel():
+                    a = torch.relu(linear(h[rows].contiguous(), self.up[e], self.rt))
+                    out[rows] = linear(a, self.down[e], self.rt)
+            return out
+
+    class InterpolatedRope:
+        def __init__(self, params, head_dim, rt):
+            self.rotary_dim = int(params["rotary_dim"])
+            r = self.rotary_dim
+            inv = 1.0 / (float(params["theta"]) ** (torch.arange(0, r, 2, dtype=torch.int64).to(torch.float32) / r))
+            self.inv_freq = (inv / float(params["factor"])).to(rt.device)
+
+    class ToyConfig:
+        def __init__(self, raw):
+            self.raw = dict(raw)
+
+        def to_dict(self):
+            return dict(self.raw)
+
+        def model_spec(self):
+            r = self.raw
+            H_, V = r["hidden_size"], r["vocab_size"]
+            norm = PartSpec("rmsnorm", {"size": H_, "eps": 1e-5})
+
+            def attn(pos):
+                return PartSpec("attention", {"hidden_size": H_, "num_heads": 3, "num_kv_heads": 3, "head_dim": 16,
+                                              "scale": 0.25, "window": None, "qk_norm": None, "position": pos})
+            stock_pos = PartSpec("rope", {"rotary_dim": 16, "theta": 1e4})
+            toy_pos = PartSpec("toy_interpolated_rope", {"rotary_dim": 16, "theta": 1e4, "factor": 4.0})
+            dense = PartSpec("swiglu", {"hidden_size": H_, "intermediate_size": 64})
+            routed = PartSpec("toy_routed", {"hidden_size": H_})
+            parts = [(attn(stock_pos), dense), (attn(toy_pos), routed), (attn(toy_pos), dense)]
+            layers = tuple(LayerSpec("prenorm", m, f, norm, norm, f"l{i}.attn.", f"l{i}.ffn.", f"l{i}.n1.", f"l{i}.n2.")
+                           for i, (m, f) in enumerate(parts))
+            return ModelSpec("ToyRoutedForCausalLM", V, H_, 256, PartSpec("embedding", {"vocab_size": V, "hidden_size": H_}),
+                             layers, tuple(RunStep(i) for i in range(3)), norm,
+                             PartSpec("lm_head", {"vocab_size": V, "hidden_size": H_, "tied": False}),
+                             embedding_prefix="emb.", final_norm_prefix="fn.", head_prefix="head.")
+
+    register_ffn("toy_routed", RoutedFFN)
+    register_position("toy_interpolated_rope", InterpolatedRope)
+    register_architecture("ToyRoutedForCausalLM", ToyConfig)
+    try:
+        raw = {"architectures": ["ToyRoutedForCausalLM"], "hidden_size": 48, "vocab_size": 131}
+        eng = Engine.from_config(raw, seed=9, std=0.2, dtype="float32", max_batch=2, max_seq_len=128, max_tokens=256)
+        n = 30
+        toks = torch.randint(0, 131, (n,), generator=torch.Generator().manual_seed(2)).tolist()
+        with torch.inference_mode():
+            s = eng.cache.open_sequences(1)
+            whole = eng.stepper.step(s, [toks], [list(range(n))]).cpu()
+            eng.cache.close_sequences(s)
+            s = eng.cache.open_sequences(1)
+            parts = [eng.stepper.step(s, [toks[:11]], [list(range(11))]).cpu()]
+            for t in toks[11:]:
+                parts.append(eng.stepper.step(s, [[t]], [[0]]).cpu())
+            eng.cache.close_sequences(s)
+            s = eng.cache.open_sequences(2)
+            both = eng.stepper.step(s, [toks, toks[:7]], [list(range(n)), [6]]).cpu()
+            eng.cache.close_sequences(s)
+        assert torch.isfinite(whole).all()
+        assert H.rel_err(torch.cat(parts), whole) <= H.FP32_TOL
+        assert H.rel_err(both[:n], whole) <= H.FP32_TOL and H.rel_err(both[n:], whole[6:7]) <= H.FP32_TOL
+
+        # plain evaluation of the same model from the engine's own tensors, whole sequence, no cache
+        m = eng.model
+        x = P.embed(torch.tensor(toks), m.embedding.table.float().cpu(), torch.float32)
+        pos = torch.arange(n)
+        used = set()
+        for blk, factor in zip(m.blocks, (1.0, 4.0, 4.0)):
+            at, ff = blk.mixer, blk.ffn
+            h = P.rmsnorm(x, blk.norm_mixer.weight.cpu(), 1e-5)
+            qkv = h @ at.w_qkv.float().cpu().T
+            q, k, v = (t.view(n, 3, 16) for t in qkv.split([48, 48, 48], dim=-1))
+            inv = 1.0 / (1e4 ** (torch.arange(0, 16, 2, dtype=torch.int64).float() / 16)) / factor
+            ang = pos.float()[:, None] * inv[None, :]
+            cos, sin = torch.cat((ang.cos(), ang.cos()), -1)[:, None, :], torch.cat((ang.sin(), ang.sin()), -1)[:, None, :]
+            rot = lambda t: t * cos + torch.cat((-t[..., 8:], t[..., :8]), -1) * sin
+            q, k = rot(q), rot(k)
+            sc = torch.einsum("qhd,khd->hqk", q, k) * 0.25
+            sc = sc.masked_fill(torch.ones(n, n, dtype=torch.bool).triu(1), float("-inf"))
+            o = torch.einsum("hqk,khd->qhd", torch.softmax(sc, -1), v).reshape(n, 48)
+            x = x + o @ at.w_o.float().cpu().T
+            h = P.rmsnorm(x, blk.norm_ffn.weight.cpu(), 1e-5)
+            if hasattr(ff, "router"):
+                choice = (h @ ff.router.float().cpu().T).argmax(-1)
+                used |= set(choice.tolist())
+                y = torch.stack([torch.relu(h[i] @ ff.up[int(e)].float().cpu().T) @ ff.down[int(e)].float().cpu().T
+                                 for i, e in enumerate(choice)])
+            else:
+                gu = h @ ff.w_gate_up.float().cpu().T
+                y = P.silu_mul(gu[:, :64], gu[:, 64:]) @ ff.w_down.float().cpu().T
+            x = x + y
+        logits = P.rmsnorm(x, m.final_norm.weight.cpu(), 1e-5) @ m.head.weight.float().cpu().T
+        assert len(used) >= 2, "the routing must send tokens to different experts for the test to mean anything"
+        assert H.rel_err(whole, logits) <= 5 * H.FP32_TOL
+    finally:
+        FFNS.unregister("toy_routed")
+        POSITIONS.unregister("toy_interpolated_rope")
+        unregister_architecture("ToyRoutedForCausalLM")
