@@ -55,7 +55,7 @@ constexpr size_t Q_BYTES = (size_t)(16 + 2) * KS * 2;      // 16 query rows, the
 template <int NWARP, int STAGES> struct Shape {
   static constexpr int THREADS = NWARP * 32;
   static constexpr size_t WARP_STAGE_BYTES = (size_t)STAGES * 2 * SLICE * KS * 2;
-  static constexpr size_t COMBINE_BYTES = (size_t)NWARP * 16 * 2 * 4 + (size_t)NWARP * G * D * 4;
+  static constexpr size_t COMBINE_BYTES = (size_t)NWARP * 16 * 2 * 4 + (size_t)NWARP * G * D * 4 + (size_t)G * D * 4 + (size_t)G * 2 * 4;
   static constexpr size_t PIPE_BYTES = NWARP * WARP_STAGE_BYTES;
   static constexpr size_t SMEM_BYTES = Q_BYTES + (PIPE_BYTES > COMBINE_BYTES ? PIPE_BYTES : COMBINE_BYTES);
 };
@@ -84,6 +84,17 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   return *reinterpret_cast<unsigned*>(&v);
 }
 __device__ __forceinline__ float bfr(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// a float of block `rank`'s shared memory at the same offset as `local` (between two cluster barriers)
+__device__ __forceinline__ float ld_remote(const float* local, unsigned rank) {
+  unsigned raddr;
+  float v;
+  asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(raddr) : "r"((unsigned)__cvta_generic_to_shared(local)), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(raddr));
+  return v;
+}
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
@@ -171,6 +182,7 @@ struct Params {
   bf16* out;                                  // [rows, nH * D]
   float* part_o; float* part_ml; int* tickets;  // [rows, nKV, S, G, D], [rows, nKV, S, G, 2], [rows * nKV]
   int nKV; int n_splits; float scale; int window; int R; float eps; int has_norm; int write_kv;
+  int cluster;   // the splits of a (row, kv head) are the blocks of one thread-block cluster
 };
 
 template <int NWARP, int STAGES>
@@ -406,6 +418,8 @@ __global__ void __launch_bounds__(NWARP * 32) attn_decode_kernel(const Params p)
     if (g + 8 < G) { wacc[(warp * G + g + 8) * D + d] = o_acc[j][2]; wacc[(warp * G + g + 8) * D + d + 1] = o_acc[j][3]; }
   }
   __syncthreads();
+  float* bp_num = wacc + NWARP * G * D;   // [G][D] this block's partial (cluster mode)
+  float* bp_ml = bp_num + G * D;          // [G][2] its maximum and sum
   const size_t pidx = ((size_t)n * p.nKV + kvh) * p.n_splits + split;
   for (int i = tid; i < G * D; i += THREADS) {
     const int h = i / D, d = i % D;
@@ -423,12 +437,38 @@ __global__ void __launch_bounds__(NWARP * 32) attn_decode_kernel(const Params p)
     }
     if (p.n_splits == 1) {
       p.out[((size_t)n * nH + kvh * G + h) * D + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+    } else if (p.cluster) {
+      bp_num[i] = num;  // relative to mx
+      if (d == 0) { bp_ml[h * 2] = mx; bp_ml[h * 2 + 1] = den; }
     } else {
       p.part_o[(pidx * G + h) * D + d] = num;  // relative to mx
       if (d == 0) { p.part_ml[(pidx * G + h) * 2] = mx; p.part_ml[(pidx * G + h) * 2 + 1] = den; }
     }
   }
   if (p.n_splits == 1) {
+    DRYFT_TRACE_PUT(1u, tr0, tr1, tr2);
+    return;
+  }
+  if (p.cluster) {
+    // ---- the splits are the blocks of one cluster: every block combines a slice of the outputs over
+    // all blocks' partials, in split order, reading them through distributed shared memory ----
+    cluster_sync_all();
+    const int per = (G * D + p.n_splits - 1) / p.n_splits;
+    for (int i = split * per + tid; i < min((split + 1) * per, G * D); i += THREADS) {
+      const int h = i / D, d = i % D;
+      float mx = -INFINITY;
+      for (int s2 = 0; s2 < p.n_splits; ++s2) mx = fmaxf(mx, ld_remote(bp_ml + h * 2, (unsigned)s2));
+      float num = 0.f, den = 0.f;
+      for (int s2 = 0; s2 < p.n_splits; ++s2) {
+        const float m = ld_remote(bp_ml + h * 2, (unsigned)s2);
+        if (m == -INFINITY) continue;
+        const float sc = exp2f(m - mx);
+        num += sc * ld_remote(bp_num + i, (unsigned)s2);
+        den += sc * ld_remote(bp_ml + h * 2 + 1, (unsigned)s2);
+      }
+      p.out[((size_t)n * nH + kvh * G + h) * D + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
+    }
+    cluster_sync_all();   // nobody leaves while another block may still read its partial
     DRYFT_TRACE_PUT(1u, tr0, tr1, tr2);
     return;
   }
@@ -481,6 +521,7 @@ __global__ void __launch_bounds__(NWARP * 32) attn_decode_kernel(const Params p)
 template <int NWARP, int STAGES>
 static int launch_shape(const Params& p, int n_rows, int nKV, int n_splits, int pdl, cudaStream_t st) {
   typedef Shape<NWARP, STAGES> S;
+  if (S::SMEM_BYTES > 227 * 1024) return DRYFT_ERR_UNSUPPORTED;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(n_rows, nKV, n_splits);
   cfg.blockDim = dim3(S::THREADS);
@@ -492,11 +533,22 @@ static int launch_shape(const Params& p, int n_rows, int nKV, int n_splits, int 
   }
   cfg.dynamicSmemBytes = S::SMEM_BYTES;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attr[2];
+  int n_attr = 0;
+  if (pdl) {
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attr;
+  }
+  if (p.cluster) {
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = 1;
+    attr[n_attr].val.clusterDim.y = 1;
+    attr[n_attr].val.clusterDim.z = (unsigned)n_splits;
+    ++n_attr;
+  }
   cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
+  cfg.numAttrs = n_attr;
   cudaError_t e = cudaLaunchKernelEx(&cfg, attn_decode_kernel<NWARP, STAGES>, p);
   if (e != cudaSuccess) return (int)e;
   return launch_status();
@@ -511,16 +563,17 @@ DRYFT_API int dryft_attn_decode(const void* qkv, int qkv_stride, const float* wq
                                 const int* tok_slot, const int* tok_pos, void* k_pages, void* v_pages,
                                 const int* page_table, int max_pages, void* out, float* part_o, float* part_ml,
                                 int* tickets, int n_rows, int nKV, int n_splits, float scale, int window, int R, float eps,
-                                int has_norm, int write_kv, int pdl, int shape, cudaStream_t st) {
+                                int has_norm, int write_kv, int pdl, int shape, int cluster, cudaStream_t st) {
   if (n_rows <= 0) return 0;
   if (n_splits < 1 || nKV < 1 || nKV > 65535 || n_splits > 64 || (R & 1) || R > D || R < 0) return DRYFT_ERR_UNSUPPORTED;
-  if (n_splits > 1 && (!part_o || !part_ml || !tickets)) return DRYFT_ERR_UNSUPPORTED;
+  if (cluster && (n_splits < 2 || n_splits > 8)) cluster = 0;
+  if (n_splits > 1 && !cluster && (!part_o || !part_ml || !tickets)) return DRYFT_ERR_UNSUPPORTED;
   Params p;
   p.qkv = (const bf16*)qkv; p.qkv_stride = qkv_stride; p.wq = wq; p.wk = wk; p.inv_freq = inv_freq;
   p.tok_slot = tok_slot; p.tok_pos = tok_pos; p.k_pages = (bf16*)k_pages; p.v_pages = (bf16*)v_pages;
   p.page_table = page_table; p.max_pages = max_pages; p.out = (bf16*)out; p.part_o = part_o; p.part_ml = part_ml;
   p.tickets = tickets; p.nKV = nKV; p.n_splits = n_splits; p.scale = scale; p.window = window; p.R = R; p.eps = eps;
-  p.has_norm = has_norm; p.write_kv = write_kv;
+  p.has_norm = has_norm; p.write_kv = write_kv; p.cluster = cluster;
   if (shape < 0) {
     // the widest block shape whose grid is resident at once (no second wave): 8, 4 or 2 warps
     static int sms = 0;
@@ -531,9 +584,10 @@ DRYFT_API int dryft_attn_decode(const void* qkv, int qkv_stride, const float* wq
     }
     const long long blocks = (long long)n_rows * nKV * n_splits;
     const long long usable = 227 * 1024;
-    const long long per_sm_8 = usable / (long long)(Shape<8, 2>::SMEM_BYTES + 1024);
+    const long long per_sm_8 = usable / (long long)(Shape<8, 2>::SMEM_BYTES + 1024);   // 0: does not fit at all
     const long long per_sm_4 = usable / (long long)(Shape<4, 2>::SMEM_BYTES + 1024);
-    shape = blocks <= sms * (per_sm_8 < 1 ? 1 : per_sm_8) ? 0 : (blocks <= sms * per_sm_4 ? 1 : 2);
+    shape = (per_sm_8 >= 1 && blocks <= sms * per_sm_8) ? 0 : ((per_sm_4 >= 1 && blocks <= sms * per_sm_4) ? 1 : 2);
+    if (shape == 2 && (long long)(Shape<2, 2>::SMEM_BYTES + 1024) > usable) shape = per_sm_4 >= 1 ? 1 : 0;
   }
   return shape == 1 ? launch_shape<4, 2>(p, n_rows, nKV, n_splits, pdl, st)
        : shape == 2 ? launch_shape<2, 2>(p, n_rows, nKV, n_splits, pdl, st)

@@ -180,7 +180,7 @@ def attention_decode_lib(head_dim: int, group: int, page: int) -> ctypes.CDLL:
                                        {"DRYFT_HEAD_DIM": head_dim, "DRYFT_GROUP": group, "DRYFT_PAGE": page})
             lib = _load(path)
             lib.dryft_attn_decode.argtypes = [_p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _i, _p, _p, _p, _p, _i, _i, _i, _f, _i,
-                                              _i, _f, _i, _i, _i, _i, _p]
+                                              _i, _f, _i, _i, _i, _i, _i, _p]
             lib.dryft_attn_decode.restype = _i
             _variants[key] = lib
         return lib
@@ -460,11 +460,13 @@ def attn_rows(q, k_pages, v_pages, page_table, tok_slot, tok_pos, out, scale: fl
 def attn_decode(qkv, q_norm_w, k_norm_w, inv_freq, tok_slot, tok_pos, k_pages, v_pages, page_table, out,
                 n_heads: int, n_kv_heads: int, head_dim: int, rotary_dim: int, eps: float, scale: float,
                 window: Optional[int], n_splits: int, part_o=None, part_ml=None, write_kv: bool = True, pdl: bool = False,
-                shape: int = -1) -> None:
+                shape: int = -1, cluster: bool = True) -> None:
     """One launch for a decode step's attention (bfloat16): per-head q/k norm + RoPE of each row's new
     token, its K/V written into the cache, attention of its query heads over the cache, splits combined.
     ``shape``: warps per block, 0 / 1 / 2 for 8 / 4 / 2; -1 lets the launcher take the widest whose grid is
-    resident at once."""
+    resident at once.  ``cluster``: with 2..8 splits the splits of a (row, kv head) run as one thread-block
+    cluster and are combined through distributed shared memory (no partial buffers needed); with more
+    splits, or ``cluster=False``, they meet in ``part_o`` / ``part_ml`` and the last block to finish combines."""
     n = qkv.shape[0]
     width = (n_heads + (2 * n_kv_heads if write_kv else 0)) * head_dim
     _need(qkv, "qkv", torch.bfloat16, (n, width))
@@ -485,7 +487,8 @@ def attn_decode(qkv, q_norm_w, k_norm_w, inv_freq, tok_slot, tok_pos, k_pages, v
     if n_heads % n_kv_heads:
         raise KernelError(f"attn_decode: {n_heads} query heads are not a multiple of {n_kv_heads} kv heads")
     tk = None
-    if n_splits > 1:
+    use_cluster = bool(cluster) and 2 <= n_splits <= 8
+    if n_splits > 1 and not use_cluster:
         _need(part_o, "part_o", torch.float32)
         _need(part_ml, "part_ml", torch.float32)
         if part_o.numel() < n * n_heads * n_splits * head_dim or part_ml.numel() < n * n_heads * n_splits * 2:
@@ -495,7 +498,7 @@ def attn_decode(qkv, q_norm_w, k_norm_w, inv_freq, tok_slot, tok_pos, k_pages, v
     _ok(lib.dryft_attn_decode(_ptr(qkv), width, _ptr(q_norm_w), _ptr(k_norm_w), _ptr(inv_freq), _ptr(tok_slot), _ptr(tok_pos),
                               _ptr(k_pages), _ptr(v_pages), _ptr(page_table), page_table.shape[1], _ptr(out), _ptr(part_o),
                               _ptr(part_ml), _ptr(tk), n, n_kv_heads, n_splits, float(scale), int(window or 0),
-                              int(rotary_dim), float(eps), int(has_norm), int(write_kv), int(pdl), int(shape), _stream()),
+                              int(rotary_dim), float(eps), int(has_norm), int(write_kv), int(pdl), int(shape), int(use_cluster), _stream()),
         f"attn_decode (head_dim {head_dim})")
 
 

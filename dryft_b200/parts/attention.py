@@ -99,12 +99,22 @@ class Attention:
         want = math.ceil(2 * self.rt.sm_count / max(1, n_rows * self.n_kv))
         return max(1, min(32, want))
 
-    @staticmethod
-    def _decode_splits(max_kv: int) -> int:
-        """Splits of the one-launch decode attention: a block's 8 warps share up to 1,024 keys through
-        shared memory for nothing, and combining splits across blocks costs a few round trips through
-        memory, so keys are only split across blocks when sequences are longer than that."""
-        return max(1, min(32, (max(1, max_kv) + 1023) // 1024))
+    CLUSTER_SPLITS = 8   # up to this many splits run as one thread-block cluster (combined on chip)
+
+    def _decode_splits(self, max_kv: int, n_rows: int) -> int:
+        """Splits of the one-launch decode attention.  Up to eight splits of a (row, kv head) run as one
+        thread-block cluster and are combined through distributed shared memory, which costs about a
+        microsecond, so a block may take as little as three pages (192 keys: one or two 16-key slices per
+        warp) -- as long as the grid stays within one block per SM: more blocks than that take the slots in
+        which the next launch's blocks start early, which costs more than the shorter walk saves.
+        Sequences too long for that split further and meet in memory (a block then takes up to 1,024 keys)."""
+        pages = (max(1, max_kv) + self.rt.page_size - 1) // self.rt.page_size
+        room = max(1, self.rt.sm_count // max(1, n_rows * self.n_kv))
+        by_cluster = min((pages + 2) // 3, room, self.CLUSTER_SPLITS)
+        if pages <= 16 and 4 * n_rows * self.n_kv > self.rt.sm_count:
+            by_cluster = 1   # up to 1,024 keys a block's eight warps are enough unless most SMs would idle
+        by_memory = min(32, (max(1, max_kv) + 1023) // 1024)
+        return max(1, by_cluster) if by_memory <= self.CLUSTER_SPLITS else by_memory
 
     def can_fuse(self, n_rows: int, norm) -> bool:
         """Few rows, bfloat16 everywhere, widths the weight-streaming product takes."""
@@ -141,9 +151,9 @@ class Attention:
         if ctx.decode and self.use_decode_kernel:
             # one launch: q/k norm + RoPE + cache write + split attention + combine
             o = torch.empty((n, self.q_dim), dtype=h.dtype, device=dev)
-            s = self._decode_splits(ctx.max_kv)
+            s = self._decode_splits(ctx.max_kv, n)
             part_o = part_ml = None
-            if s > 1:
+            if s > self.CLUSTER_SPLITS:
                 part_o = torch.empty((n, self.n_heads, s, self.head_dim), dtype=torch.float32, device=dev)
                 part_ml = torch.empty((n, self.n_heads, s, 2), dtype=torch.float32, device=dev)
             K.attn_decode(qkv, self.q_norm_w, self.k_norm_w, self.position.inv_freq, ctx.tok_slot, ctx.tok_pos, cache.k, cache.v,

@@ -464,19 +464,21 @@ def test_attn_decode_fused(n_heads, n_kv, d, rot, window):
         kseq[pos], vseq[pos] = k_r[i], vn[i]
         refs.append(_attn_ref(q_r[i], kseq, vseq, pos, scale, window))
     ref = torch.stack(refs)
-    for splits, shape in ((1, -1), (2, 0), (7, 1), (1, 2), (3, 2), (1, 1)):
+    # (splits, block shape, splits combined inside a thread-block cluster or through memory)
+    for splits, shape, cluster in ((1, -1, True), (2, 0, True), (7, 1, True), (1, 2, True), (3, 2, False), (5, -1, True),
+                                   (8, 2, True), (7, 0, False), (12, 1, True)):
         old = {s: (kv[0][:lens[s]], kv[1][:lens[s]]) for s, kv in seqs.items()}
         # pages for L+1 tokens, only L filled; the rest is a canary the kernel must not touch
         kc, vc, pt = _fill_cache({s: (torch.cat([kv[0], torch.full((1, n_kv, d), 55.0).to(dtype)]),
                                       torch.cat([kv[1], torch.full((1, n_kv, d), 55.0).to(dtype)])) for s, kv in old.items()},
-                                 n_kv, d, page, dtype, n_pages=16, max_pages=5, slots=6, scatter_seed=splits + shape)
+                                 n_kv, d, page, dtype, n_pages=16, max_pages=5, slots=6, scatter_seed=splits + shape + 2 * cluster)
         kc0, vc0 = kc.clone(), vc.clone()
         out = torch.full((n, n_heads * d), 9.0, device=DEV, dtype=dtype)
         po = torch.empty(n, n_heads, splits, d, device=DEV) if splits > 1 else None
         pm = torch.empty(n, n_heads, splits, 2, device=DEV) if splits > 1 else None
         i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
         k.attn_decode(qkv.to(DEV), wq.to(DEV), wk.to(DEV), inv_freq.to(DEV), i32([r[0] for r in rows]), i32([r[1] for r in rows]),
-                      kc, vc, pt, out, n_heads, n_kv, d, rot, eps, scale, window, splits, po, pm, shape=shape)
+                      kc, vc, pt, out, n_heads, n_kv, d, rot, eps, scale, window, splits, po, pm, shape=shape, cluster=cluster)
         assert torch.isfinite(out.float()).all()
         torch.testing.assert_close(out.cpu().float(), ref, rtol=2e-2, atol=2e-2)
         changed_k = (kc != kc0).any(dim=-1)
