@@ -7,6 +7,7 @@ model, ``--seed``, ``--samples``, ``--workload name,b,in,out``.  Token ids in an
     python -m dryft_b200 generate --tiny --workload demo,3,9,8 --temperature 0.7 --top-k 20 --seed 1
     python -m dryft_b200 bench --model DIR --workload b1,1,512,32 --workload b16,16,512,128 --samples 5
     python -m dryft_b200 random-model --preset tiny-b --seed 1 --out DIR
+    python -m dryft_b200 replay --model DIR --dtype float32 --out DIR --max-tokens 4096 < trace.jsonl
 """
 
 from __future__ import annotations
@@ -37,7 +38,7 @@ def _model_dir(args) -> str:
             write_random_model(preset("tiny-a"), 0, d, std=0.08)
         return d
     if not args.model:
-        raise SystemExit("give --model DIR (or set DRYFT_MODEL_PATH), or --tiny")
+        raise SystemExit("give --model DIR (or set DRYFT_MODEL_PATH), --preset NAME, or --tiny")
     return args.model
 
 
@@ -52,6 +53,11 @@ def _engine(args):
     if args.tiny:
         kw.setdefault("max_batch", 8)
         kw.setdefault("max_seq_len", 128)
+    if getattr(args, "preset", None) and not args.tiny and not args.model:
+        # random weights of a named shape, made on the device (no folder is written)
+        from .config import preset
+
+        return Engine.from_config(preset(args.preset), seed=args.weights_seed, **kw)
     return Engine(_model_dir(args), **kw)
 
 
@@ -64,7 +70,10 @@ def cmd_generate(args) -> int:
         prompts += [[rng.randrange(eng.config.vocab_size) for _ in range(inp)] for _ in range(b)]
     if not prompts:
         raise SystemExit("nothing to generate from: give --prompt-ids or --workload")
-    n = args.max_new_tokens if not args.workload else max(args.max_new_tokens, max(_workload(w)[3] for w in args.workload))
+    if args.max_new_tokens is not None:
+        n = args.max_new_tokens
+    else:
+        n = max((_workload(w)[3] for w in args.workload), default=16)   # a workload names its own output length
     out = eng.generate_many(prompts, n, temperature=args.temperature, top_k=args.top_k, seed=args.seed,
                             stop_token_ids=args.stop_token_id)
     for p, o in zip(prompts, out):
@@ -121,6 +130,8 @@ def main(argv=None) -> int:
     def common(p):
         p.add_argument("--model", default=os.environ.get("DRYFT_MODEL_PATH"))
         p.add_argument("--tiny", action="store_true", help="a random tiny Qwen3 instead of --model")
+        p.add_argument("--preset", default=None, help="random weights of a named shape instead of --model (tiny-a, tiny-b, qwen3-4b, ...)")
+        p.add_argument("--weights-seed", type=int, default=0, help="seed of --preset's weights")
         p.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
         p.add_argument("--seed", type=int, default=0)
         p.add_argument("--workload", action="append", default=[], help="name,b,in,out")
@@ -131,7 +142,7 @@ def main(argv=None) -> int:
     g = sub.add_parser("generate", help="generate token ids from token ids")
     common(g)
     g.add_argument("--prompt-ids", action="append", default=[], help="comma-separated token ids; may repeat")
-    g.add_argument("--max-new-tokens", type=int, default=16)
+    g.add_argument("--max-new-tokens", type=int, default=None, help="default: the workloads' output length, else 16")
     g.add_argument("--temperature", type=float, default=0.0)
     g.add_argument("--top-k", type=int, default=0)
     g.add_argument("--stop-token-id", type=int, action="append", default=[])
@@ -142,6 +153,9 @@ def main(argv=None) -> int:
     b.add_argument("--samples", type=int, default=5)
     b.set_defaults(fn=cmd_bench)
 
+    t = sub.add_parser("replay", help="feed a token trace step by step and write logits (bin/trace_run)", add_help=False)
+    t.set_defaults(fn=None)
+
     r = sub.add_parser("random-model", help="write a model folder with random weights")
     r.add_argument("--preset", default=None)
     r.add_argument("--config", default=None, help="a config.json to take the sizes from")
@@ -151,6 +165,11 @@ def main(argv=None) -> int:
     r.add_argument("--out", required=True)
     r.set_defaults(fn=cmd_random_model)
 
+    argv = list(sys.argv[1:] if argv is None else argv)
+    if argv[:1] == ["replay"]:   # the replay program parses its own options (those of bin/trace_run)
+        from .replay import main as replay_main
+
+        return replay_main(argv[1:])
     args = ap.parse_args(argv)
     return args.fn(args)
 
