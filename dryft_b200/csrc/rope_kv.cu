@@ -19,6 +19,7 @@
 // (rope_table_kernel: [token][cos | sin][R/2], already rounded to T) and every layer's launch reads
 // the table; without a table each warp evaluates its own.
 #include "common.cuh"
+#include <type_traits>
 
 // two consecutive elements of T <-> two floats
 template <typename T> __device__ __forceinline__ void load2(const T* p, float& a, float& b);
@@ -337,20 +338,38 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) qk_norm_rope_store_fast_kerne
     for (int i = 0; i < NP; ++i) {
       const int j = 2 * lane + 64 * i;
       if (j < half) {
-        float o1[2], o2[2];
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          float x = a[u][i][e], y = b[u][i][e];
+        if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+          // the same roundings on pairs: x * inv in 32-bit rounded to a bfloat16 pair; every bfloat16
+          // product and sum below is the exact result rounded once (the _rn forms are never fused)
+          const __nv_bfloat162 cs2 = __floats2bfloat162_rn(cs[i][0], cs[i][1]), sn2 = __floats2bfloat162_rn(sn[i][0], sn[i][1]);
+          __nv_bfloat162 x2, y2;
           if (has_norm) {
-            x = rnd<T>(rnd<T>(x * inv[u]) * (is_q ? wa[0][i][e] : wa[1][i][e]));
-            y = rnd<T>(rnd<T>(y * inv[u]) * (is_q ? wb[0][i][e] : wb[1][i][e]));
+            const __nv_bfloat162 wa2 = is_q ? __floats2bfloat162_rn(wa[0][i][0], wa[0][i][1]) : __floats2bfloat162_rn(wa[1][i][0], wa[1][i][1]);
+            const __nv_bfloat162 wb2 = is_q ? __floats2bfloat162_rn(wb[0][i][0], wb[0][i][1]) : __floats2bfloat162_rn(wb[1][i][0], wb[1][i][1]);
+            x2 = __hmul2_rn(__floats2bfloat162_rn(a[u][i][0] * inv[u], a[u][i][1] * inv[u]), wa2);
+            y2 = __hmul2_rn(__floats2bfloat162_rn(b[u][i][0] * inv[u], b[u][i][1] * inv[u]), wb2);
+          } else {
+            x2 = __floats2bfloat162_rn(a[u][i][0], a[u][i][1]);
+            y2 = __floats2bfloat162_rn(b[u][i][0], b[u][i][1]);
           }
-          // separate roundings of the two products, then of the sum (no fused multiply-add across them)
-          o1[e] = __fadd_rn(rnd<T>(__fmul_rn(x, cs[i][e])), -rnd<T>(__fmul_rn(y, sn[i][e])));
-          o2[e] = __fadd_rn(rnd<T>(__fmul_rn(y, cs[i][e])), rnd<T>(__fmul_rn(x, sn[i][e])));
+          *reinterpret_cast<__nv_bfloat162*>(dst + j) = __hsub2_rn(__hmul2_rn(x2, cs2), __hmul2_rn(y2, sn2));
+          *reinterpret_cast<__nv_bfloat162*>(dst + j + half) = __hadd2_rn(__hmul2_rn(y2, cs2), __hmul2_rn(x2, sn2));
+        } else {
+          float o1[2], o2[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            float x = a[u][i][e], y = b[u][i][e];
+            if (has_norm) {
+              x = rnd<T>(rnd<T>(x * inv[u]) * (is_q ? wa[0][i][e] : wa[1][i][e]));
+              y = rnd<T>(rnd<T>(y * inv[u]) * (is_q ? wb[0][i][e] : wb[1][i][e]));
+            }
+            // separate roundings of the two products, then of the sum (no fused multiply-add across them)
+            o1[e] = __fadd_rn(rnd<T>(__fmul_rn(x, cs[i][e])), -rnd<T>(__fmul_rn(y, sn[i][e])));
+            o2[e] = __fadd_rn(rnd<T>(__fmul_rn(y, cs[i][e])), rnd<T>(__fmul_rn(x, sn[i][e])));
+          }
+          store2<T>(dst + j, o1[0], o1[1]);
+          store2<T>(dst + j + half, o2[0], o2[1]);
         }
-        store2<T>(dst + j, o1[0], o1[1]);
-        store2<T>(dst + j + half, o2[0], o2[1]);
       }
     }
   }
