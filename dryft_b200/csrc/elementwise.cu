@@ -132,7 +132,7 @@ template <typename T> __device__ __forceinline__ void store_vec(T* p, const floa
 
 template <typename T>
 __global__ void rmsnorm_kernel(const T* x, const T* __restrict__ delta, const float* __restrict__ w,
-                               const int* __restrict__ rows, T* x_out, T* __restrict__ h, int hidden, float eps) {
+                               const int* __restrict__ rows, T* x_out, T* __restrict__ h, int hidden, float eps, int aligned) {
   // x and x_out may be the same buffer (in-place residual update): no __restrict__ on them
   extern __shared__ __align__(16) float row[];  // hidden floats + 33 scratch
   float* scratch = row + ((hidden + 3) & ~3);
@@ -143,7 +143,7 @@ __global__ void rmsnorm_kernel(const T* x, const T* __restrict__ delta, const fl
   T* xo = x_out ? x_out + (size_t)src * hidden : nullptr;
   T* hr = h + (size_t)r * hidden;
   constexpr int V = Vec16<T>::N;
-  const bool vec = hidden % V == 0;  // rows are then 16-byte aligned too (allocations are)
+  const bool vec = aligned && hidden % V == 0;  // every row then starts on a 16-byte boundary
   float ss = 0.f;
   if (vec) {
     for (int i = threadIdx.x * V; i < hidden; i += blockDim.x * V) {
@@ -222,9 +222,12 @@ __global__ void rmsnorm_rows_kernel(const T* x, const T* __restrict__ delta, con
   for (int k = 0; k < RMS_REG_VECS; ++k) {
     const int i = (threadIdx.x + k * blockDim.x) * V;
     if (i < hidden) {
-      float o[V];
+      float o[V], wv[V];
 #pragma unroll
-      for (int e = 0; e < V; ++e) o[e] = w[i + e] * rnd<T>(v[k][e] * inv);
+      for (int e = 0; e < V; e += 4)   // the weight in 16-byte pieces (hidden % V == 0 and allocations are aligned)
+        *reinterpret_cast<float4*>(wv + e) = __ldg(reinterpret_cast<const float4*>(w + i + e));
+#pragma unroll
+      for (int e = 0; e < V; ++e) o[e] = wv[e] * rnd<T>(v[k][e] * inv);
       if (xo) store_vec<T>(xo + i, v[k]);
       store_vec<T>(hr + i, o);
     }
@@ -236,7 +239,9 @@ static int rmsnorm_launch(const void* x, const void* delta, const float* w, cons
                           int n_rows, int hidden, float eps, cudaStream_t st) {
   if (n_rows <= 0) return 0;
   constexpr int V = Vec16<T>::N;
-  if (n_rows >= 256 && hidden % V == 0 && hidden / V <= RMS_REG_VECS * 1024) {
+  // 16-byte accesses need every base address on a 16-byte boundary (and hidden % V == 0 for the rows)
+  const int aligned = !(((uintptr_t)x | (uintptr_t)delta | (uintptr_t)w | (uintptr_t)x_out | (uintptr_t)h) & 15);
+  if (aligned && n_rows >= 256 && hidden % V == 0 && hidden / V <= RMS_REG_VECS * 1024) {
     const int vecs = hidden / V;
     int threads = ((vecs + RMS_REG_VECS - 1) / RMS_REG_VECS + 31) & ~31;
     if (threads < 64) threads = 64;
@@ -252,7 +257,7 @@ static int rmsnorm_launch(const void* x, const void* delta, const float* w, cons
     attr_bytes = smem;
   }
   int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-  rmsnorm_kernel<T><<<n_rows, threads, smem, st>>>((const T*)x, (const T*)delta, w, rows, (T*)x_out, (T*)h, hidden, eps);
+  rmsnorm_kernel<T><<<n_rows, threads, smem, st>>>((const T*)x, (const T*)delta, w, rows, (T*)x_out, (T*)h, hidden, eps, aligned);
   return launch_status();
 }
 DRYFT_API int dryft_rmsnorm(int is_bf16, const void* x, const void* delta, const float* w, const int* rows, void* x_out,
@@ -315,7 +320,7 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ gu, T* __restrict__ y,
 template <typename T>
 static int silu_launch(const void* gu, void* y, int rows, int inter, cudaStream_t st) {
   constexpr int V = Vec16<T>::N;
-  if (inter % V == 0) {
+  if (inter % V == 0 && !(((uintptr_t)gu | (uintptr_t)y) & 15)) {   // 16-byte accesses
     size_t total = (size_t)rows * (inter / V);
     silu_mul_vec_kernel<T><<<(unsigned)((total + 255) / 256), 256, 0, st>>>((const T*)gu, (T*)y, inter, total);
   } else {
