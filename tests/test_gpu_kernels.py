@@ -426,7 +426,8 @@ def test_attn_rows(dtype, n_heads, n_kv, d, window):
         torch.testing.assert_close(out.cpu().float(), ref, rtol=rt, atol=at)
 
 
-@pytest.mark.parametrize("n_heads,n_kv,d,rot", [(4, 2, 16, 16), (6, 2, 48, 48), (8, 2, 128, 128), (5, 5, 64, 32), (16, 1, 32, 32)])
+@pytest.mark.parametrize("n_heads,n_kv,d,rot", [(4, 2, 16, 16), (6, 2, 48, 48), (8, 2, 128, 128), (5, 5, 64, 32), (16, 1, 32, 32),
+                                                 (4, 2, 256, 256)])
 @pytest.mark.parametrize("window", [None, 70])
 def test_attn_decode_fused(n_heads, n_kv, d, rot, window):
     """The one-launch decode attention against the plain parts: q/k norm + RoPE of the new token, its
@@ -477,8 +478,14 @@ def test_attn_decode_fused(n_heads, n_kv, d, rot, window):
         po = torch.empty(n, n_heads, splits, d, device=DEV) if splits > 1 else None
         pm = torch.empty(n, n_heads, splits, 2, device=DEV) if splits > 1 else None
         i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
-        k.attn_decode(qkv.to(DEV), wq.to(DEV), wk.to(DEV), inv_freq.to(DEV), i32([r[0] for r in rows]), i32([r[1] for r in rows]),
-                      kc, vc, pt, out, n_heads, n_kv, d, rot, eps, scale, window, splits, po, pm, shape=shape, cluster=cluster)
+        run = lambda: k.attn_decode(qkv.to(DEV), wq.to(DEV), wk.to(DEV), inv_freq.to(DEV), i32([r[0] for r in rows]),
+                                    i32([r[1] for r in rows]), kc, vc, pt, out, n_heads, n_kv, d, rot, eps, scale, window,
+                                    splits, po, pm, shape=shape, cluster=cluster)
+        if d == 256 and shape == 0:
+            with pytest.raises(k.KernelError):   # eight warps' rings of 256-wide rows do not fit an SM: refused, not wrong
+                run()
+            continue
+        run()
         assert torch.isfinite(out.float()).all()
         torch.testing.assert_close(out.cpu().float(), ref, rtol=2e-2, atol=2e-2)
         changed_k = (kc != kc0).any(dim=-1)
