@@ -135,15 +135,15 @@ __device__ __forceinline__ void norm_rope_head(const bf16* __restrict__ src, con
     const int j = lane + 32 * jj;
     a[jj] = b[jj] = 0.f;
     if (j < half) {
-      a[jj] = __bfloat162float(src[j]);
-      b[jj] = __bfloat162float(src[j + half]);
+      a[jj] = ld_prev_bf16(src + j);   // the projection before this launch wrote it
+      b[jj] = ld_prev_bf16(src + j + half);
       ss += a[jj] * a[jj] + b[jj] * b[jj];
     }
   }
   float inv = 1.f;
   if (has_norm) {
     for (int i = R + lane; i < D; i += 32) {
-      const float v = __bfloat162float(src[i]);
+      const float v = ld_prev_bf16(src + i);
       ss += v * v;
     }
     ss = warp_sum(ss);
@@ -166,7 +166,7 @@ __device__ __forceinline__ void norm_rope_head(const bf16* __restrict__ src, con
     }
   }
   for (int i = R + lane; i < D; i += 32) {
-    float x = __bfloat162float(src[i]);
+    float x = ld_prev_bf16(src + i);
     if (has_norm) x = bfr(bfr(x * inv) * w[i]);
     dst[i] = __float2bfloat16_rn(x);
     if (dst2) dst2[i] = __float2bfloat16_rn(x);
@@ -292,7 +292,7 @@ __global__ void __launch_bounds__(NWARP * 32) attn_decode_kernel(const Params p)
       } else {
         const bf16* vsrc = row + (size_t)(nH + p.nKV + kvh) * D;
         for (int i = lane; i < D; i += 32) {
-          const bf16 v = vsrc[i];
+          const bf16 v = __ushort_as_bfloat16(ld_prev(reinterpret_cast<const unsigned short*>(vsrc) + i));   // written by the projection before this launch
           p.v_pages[off + i] = v;
           new_v[i] = v;
         }

@@ -29,6 +29,16 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(flo
 // Round a 32-bit intermediate to T and back: a rounding point of the bfloat16 path.
 template <typename T> __device__ __forceinline__ float rnd(float v) { return to_f32<T>(from_f32<T>(v)); }
 
+// Data that the launch before this one wrote (activations, sums of squares, the residual stream) is read
+// through L2 only in kernels that may run as programmatic dependents.  Such a grid is resident while its
+// predecessor still runs, so that data is not read-only for the grid's lifetime: the non-coherent path
+// (ld.global.nc, which the compiler also picks by itself for const __restrict__ pointers) may return lines
+// that an earlier grid left in this SM's L1.  Weights never change and keep the cached paths.
+template <typename T> __device__ __forceinline__ T ld_prev(const T* p) { return __ldcg(p); }
+__device__ __forceinline__ float ld_prev_bf16(const __nv_bfloat16* p) {
+  return __bfloat162float(__ushort_as_bfloat16(__ldcg(reinterpret_cast<const unsigned short*>(p))));
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

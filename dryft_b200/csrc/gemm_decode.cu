@@ -19,6 +19,13 @@
 // stay in shared memory; otherwise they are read through L1.  The 8 partial sums are added in warp
 // order through shared memory: a row's result depends neither on the other rows nor on M.
 //
+// The norm can also be split between two launches, which takes it off the consumer's critical path: a
+// residual product that knows the next norm's weight w leaves, beside the new stream x, the weighted
+// activations xw = T(x * w); the next product then multiplies xw as plain activations (no prologue at
+// all) and scales its sums by inv[m] = rsqrt(mean(x[m]^2) + eps) in the epilogue, in 32-bit:
+// inv * sum_k T(x*w) W in place of sum_k T(T(x*inv)*w) W -- one rounding of the activations fewer than the
+// reference makes (model.py:28-32), the statistics still in 32-bit.
+//
 // The kernel may be launched as a programmatic dependent of the launch before it: it requests its
 // first weights, which depend on nothing, and only then waits for the earlier grid.
 // No block waits on another block of its grid; there is no spin in this file.
@@ -42,6 +49,9 @@ constexpr int SS_STRIDE = 64;
 constexpr int KA = K + ((64 - (K * 2) % 128 + 128) % 128) / 2;  // resident row stride: bytes = 64 mod 128
 
 enum Mode { STORE_BF16 = 0, STORE_F32 = 1, RESIDUAL = 2, SILU = 3 };
+// what happens to the activations: nothing; RMSNorm in the prologue (rows normalised into shared memory);
+// or they come weighted already (T(x * w)) and the sums are scaled by inv[m] in the epilogue
+enum Pro { PLAIN = 0, NORMED = 1, SCALED = 2 };
 
 __device__ __forceinline__ uint4 ld_stream(const void* p) {
   uint4 v;
@@ -58,10 +68,12 @@ __device__ __forceinline__ float bfr(float v) { return __bfloat162float(__float2
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
-template <int MB, int MODE, bool NORM>
+template <int MB, int MODE, int PRO>
 __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
     const bf16* __restrict__ A, int lda, const bf16* __restrict__ W, void* C, int ldc, int M, int N,
-    const float* __restrict__ norm_w, const float* __restrict__ ss_in, int ss_parts, float eps, float* __restrict__ ss_out) {
+    const float* __restrict__ norm_w, const float* __restrict__ ss_in, int ss_parts, float eps, float* __restrict__ ss_out,
+    const float* __restrict__ next_w, bf16* __restrict__ xw_out) {
+  constexpr bool NORM = PRO == NORMED;
   constexpr int MP = 8 * MB;
   constexpr int RED = WARPS * ROWS * (MP + 1);
   extern __shared__ __align__(16) unsigned char smem[];
@@ -120,6 +132,48 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
   pdl_wait();  // from here on, what earlier launches wrote (activations, sums of squares) is visible
   DRYFT_TRACE_NOW(tr1);
 
+  // SCALED: the rows' sums of squares are requested now and added after the first tile's products, so
+  // that nothing waits for them: warp w owns rows w, w + 8, ...; a lane holds up to SSL blocks per row
+  constexpr int SSL = 8;
+  float ssv[MB][SSL];
+  if (PRO == SCALED) {
+#pragma unroll
+    for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+      for (int i = 0; i < SSL; ++i) {
+        const int m = warp + 8 * mb, part = lane + 32 * i;
+        ssv[mb][i] = (m < M && part < ss_parts) ? ld_prev(ss_in + (size_t)part * SS_STRIDE + m) : 0.f;
+      }
+  }
+  bool inv_done = false;
+
+  if (PRO == SCALED) {
+    // the weighted activations go to shared memory once per block (one trip through L2, no arithmetic):
+    // every tile of the block reads them from there
+    constexpr int CHUNKS = K / 8;
+    constexpr int ITEMS = MP * CHUNKS;
+    constexpr int PER = ITEMS / THREADS;
+    constexpr int BATCH = PER <= 5 ? PER : 5;
+#pragma unroll 1
+    for (int first = 0; first < PER; first += BATCH) {
+      uint4 raw[BATCH];
+#pragma unroll
+      for (int u = 0; u < BATCH; ++u) {
+        const int i = tid + (first + u) * THREADS;
+        const int m = i / CHUNKS, c = i - m * CHUNKS;
+        raw[u] = (first + u < PER && m < M) ? ld_prev(reinterpret_cast<const uint4*>(A + (size_t)m * lda + c * 8)) : zero;
+      }
+#pragma unroll
+      for (int u = 0; u < BATCH; ++u) {
+        if (first + u >= PER) break;
+        const int i = tid + (first + u) * THREADS;
+        const int m = i / CHUNKS, c = i - m * CHUNKS;
+        *reinterpret_cast<uint4*>(a_res + (size_t)m * KA + c * 8) = raw[u];
+      }
+    }
+    __syncthreads();
+  }
+
   if (NORM) {
     // inv[m] = rsqrt(mean(x[m]^2) + eps): warp m adds the blocks of sums of squares in a fixed order;
     // then the normalised rows a[m,k] = T(T(x[m,k] * inv[m]) * w[k]) go to shared memory once per block.
@@ -136,14 +190,14 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
       for (int u = 0; u < BATCH; ++u) {
         const int i = tid + (first + u) * THREADS;
         const int m = i / CHUNKS, c = i - m * CHUNKS;
-        raw[u] = (first + u < PER && m < M) ? __ldg(reinterpret_cast<const uint4*>(A + (size_t)m * lda + c * 8)) : zero;
+                raw[u] = (first + u < PER && m < M) ? ld_prev(reinterpret_cast<const uint4*>(A + (size_t)m * lda + c * 8)) : zero;
       }
     };
     fetch(0);
     for (int m = warp; m < MP; m += WARPS) {
       float s = 0.f;
       if (m < M)
-        for (int p = lane; p < ss_parts; p += 32) s += ss_in[(size_t)p * SS_STRIDE + m];
+        for (int p = lane; p < ss_parts; p += 32) s += ld_prev(ss_in + (size_t)p * SS_STRIDE + m);
       s = warp_sum(s);
       if (lane == 0) inv_s[m] = rsqrtf(s / (float)K + eps);
     }
@@ -178,8 +232,9 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
     __syncthreads();
   }
   // this thread's activation fragments: batch row mb*8 + g, k as for the weights
-  const bf16* a_frag = NORM ? a_res + (size_t)g * KA + k_warp : A + (size_t)g * lda + k_warp;
-  const size_t a_mb = NORM ? (size_t)8 * KA : (size_t)8 * lda;
+  constexpr bool STAGED = PRO != PLAIN;   // the block's activations are in shared memory
+  const bf16* a_frag = STAGED ? a_res + (size_t)g * KA + k_warp : A + (size_t)g * lda + k_warp;
+  const size_t a_mb = STAGED ? (size_t)8 * KA : (size_t)8 * lda;
 
   DRYFT_TRACE_NOW(tr2);
   int buf = 0;
@@ -199,8 +254,8 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
 #pragma unroll
         for (int mb = 0; mb < MB; ++mb) {
           uint4 a = zero;
-          if (NORM) a = *reinterpret_cast<const uint4*>(a_frag + mb * a_mb + (chunk * CHUNK + u) * 32);
-          else if (mb * 8 + g < M) a = __ldg(reinterpret_cast<const uint4*>(a_frag + mb * a_mb + (chunk * CHUNK + u) * 32));
+          if (STAGED) a = *reinterpret_cast<const uint4*>(a_frag + mb * a_mb + (chunk * CHUNK + u) * 32);
+          else if (mb * 8 + g < M) a = ld_prev(reinterpret_cast<const uint4*>(a_frag + mb * a_mb + (chunk * CHUNK + u) * 32));
           mma16816(acc[mb], wa[u].x, wb[u].x, wa[u].y, wb[u].y, a.x, a.y);
           mma16816(acc[mb], wa[u].z, wb[u].z, wa[u].w, wb[u].w, a.z, a.w);
         }
@@ -213,6 +268,19 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
       request(w0, w1, 0);
     }
 
+    if (PRO == SCALED && !inv_done) {
+      inv_done = true;
+#pragma unroll
+      for (int mb = 0; mb < MB; ++mb) {
+        float sm = 0.f;
+#pragma unroll
+        for (int i = 0; i < SSL; ++i) sm += ssv[mb][i];
+        for (int part = lane + 32 * SSL; part < ss_parts; part += 32)   // more blocks than the registers hold
+          if (warp + 8 * mb < M) sm += ld_prev(ss_in + (size_t)part * SS_STRIDE + warp + 8 * mb);
+        sm = warp_sum(sm);
+        if (lane == 0) inv_s[warp + 8 * mb] = rsqrtf(sm / (float)K + eps);   // visible after the barrier below
+      }
+    }
     // partial sums -> shared memory (two buffers, so one barrier per tile is enough)
     float* red = red_base + buf * RED;
     buf ^= 1;
@@ -228,7 +296,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
       float s = 0.f;
 #pragma unroll
       for (int w = 0; w < WARPS; ++w) s += red[(w * ROWS + row) * (MP + 1) + m];
-      return s;
+      return PRO == SCALED ? s * inv_s[m] : s;
     };
     const int n0 = tile * TILE_N;
     if (MODE == SILU) {
@@ -249,8 +317,9 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
         const int n = n0 + row;
         float sq = 0.f;
         if (m < M && n < N) {
-          const float v = bfr(__bfloat162float(x[(size_t)m * ldc + n]) + bfr(total(row, m)));
+          const float v = bfr(ld_prev_bf16(x + (size_t)m * ldc + n) + bfr(total(row, m)));
           x[(size_t)m * ldc + n] = __float2bfloat16_rn(v);
+          if (xw_out) xw_out[(size_t)m * ldc + n] = __float2bfloat16_rn(v * next_w[n]);   // for the next norm
           sq = v * v;
         }
 #pragma unroll
@@ -269,19 +338,22 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
       }
     }
   }
-  DRYFT_TRACE_PUT((unsigned)(K * 16 + MODE * 2 + (NORM ? 1 : 0)), tr0, tr1, tr2);
+  DRYFT_TRACE_PUT((unsigned)(K * 16 + MODE * 2 + (PRO != PLAIN ? 1 : 0)), tr0, tr1, tr2);
 }
 
-template <int MB, int MODE, bool NORM>
+template <int MB, int MODE, int PRO>
 int launch3(const void* A, int lda, const void* W, void* C, int ldc, int M, int N, const float* norm_w,
-            const float* ss_in, int ss_parts, float eps, float* ss_out, int pdl, cudaStream_t st) {
+            const float* ss_in, int ss_parts, float eps, float* ss_out, const float* next_w, void* xw_out, int pdl,
+            cudaStream_t st) {
+  constexpr bool NORM = PRO == NORMED;
   constexpr int MP = 8 * MB;
   size_t smem = (size_t)2 * WARPS * ROWS * (MP + 1) * 4 + SS_STRIDE * 4;
   if (NORM) smem += (size_t)MP * KA * 2 + (size_t)K * 2;
+  if (PRO == SCALED) smem += (size_t)MP * KA * 2;
   if (smem > 110 * 1024) return DRYFT_ERR_UNSUPPORTED;
   static size_t attr_bytes = 48 * 1024;  // per instantiation; raised by an eager launch before any capture
   if (smem > attr_bytes) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_decode_kernel<MB, MODE, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_decode_kernel<MB, MODE, PRO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
     attr_bytes = smem;
   }
@@ -307,25 +379,32 @@ int launch3(const void* A, int lda, const void* W, void* C, int ldc, int M, int 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_decode_kernel<MB, MODE, NORM>, (const bf16*)A, lda, (const bf16*)W, C, ldc, M,
-                                     N, norm_w, ss_in, ss_parts, eps, ss_out);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_decode_kernel<MB, MODE, PRO>, (const bf16*)A, lda, (const bf16*)W, C, ldc, M,
+                                     N, norm_w, ss_in, ss_parts, eps, ss_out, next_w, (bf16*)xw_out);
   if (e != cudaSuccess) return (int)e;
   return launch_status();
 }
+struct Args {
+  const void* A; int lda; const void* W; void* C; int ldc; int M; int N;
+  const float* norm_w; const float* ss_in; int ss_parts; float eps; float* ss_out; const float* next_w; void* xw_out;
+  int pdl; cudaStream_t st;
+};
+template <int MB, int MODE, int PRO>
+int launch_a(const Args& a) {
+  return launch3<MB, MODE, PRO>(a.A, a.lda, a.W, a.C, a.ldc, a.M, a.N, a.norm_w, a.ss_in, a.ss_parts, a.eps, a.ss_out, a.next_w,
+                                a.xw_out, a.pdl, a.st);
+}
 template <int MB, int MODE>
-int launch2(bool norm, const void* A, int lda, const void* W, void* C, int ldc, int M, int N, const float* norm_w,
-            const float* ss_in, int ss_parts, float eps, float* ss_out, int pdl, cudaStream_t st) {
-  return norm ? launch3<MB, MODE, true>(A, lda, W, C, ldc, M, N, norm_w, ss_in, ss_parts, eps, ss_out, pdl, st)
-              : launch3<MB, MODE, false>(A, lda, W, C, ldc, M, N, norm_w, ss_in, ss_parts, eps, ss_out, pdl, st);
+int launch2(int pro, const Args& a) {
+  return pro == NORMED ? launch_a<MB, MODE, NORMED>(a) : pro == SCALED ? launch_a<MB, MODE, SCALED>(a) : launch_a<MB, MODE, PLAIN>(a);
 }
 template <int MB>
-int launch1(int mode, bool norm, const void* A, int lda, const void* W, void* C, int ldc, int M, int N,
-            const float* norm_w, const float* ss_in, int ss_parts, float eps, float* ss_out, int pdl, cudaStream_t st) {
+int launch1(int mode, int pro, const Args& a) {
   switch (mode) {
-    case STORE_BF16: return launch2<MB, STORE_BF16>(norm, A, lda, W, C, ldc, M, N, norm_w, ss_in, ss_parts, eps, ss_out, pdl, st);
-    case STORE_F32: return launch2<MB, STORE_F32>(norm, A, lda, W, C, ldc, M, N, norm_w, ss_in, ss_parts, eps, ss_out, pdl, st);
-    case RESIDUAL: return launch2<MB, RESIDUAL>(norm, A, lda, W, C, ldc, M, N, norm_w, ss_in, ss_parts, eps, ss_out, pdl, st);
-    case SILU: return launch2<MB, SILU>(norm, A, lda, W, C, ldc, M, N, norm_w, ss_in, ss_parts, eps, ss_out, pdl, st);
+    case STORE_BF16: return launch2<MB, STORE_BF16>(pro, a);
+    case STORE_F32: return launch2<MB, STORE_F32>(pro, a);
+    case RESIDUAL: return launch2<MB, RESIDUAL>(pro, a);
+    case SILU: return launch2<MB, SILU>(pro, a);
   }
   return DRYFT_ERR_UNSUPPORTED;
 }
@@ -335,15 +414,20 @@ DRYFT_API int dryft_gemm_decode_k() { return K; }
 DRYFT_TRACE_EXPORT(dryft_gemm_decode_trace)
 
 // Same contract as dryft_gemm_small_m (csrc/gemm_small_m.cu) for this library's K.  A residual product
-// of N outputs leaves ceil(N/16) blocks of sums of squares in ss_out.
+// of N outputs leaves ceil(N/16) blocks of sums of squares in ss_out and, given the next norm's weight
+// next_w [N] and xw_out [M, ldc], the weighted activations T(x * next_w) for the product after it.
+// scaled != 0: A holds such weighted activations; the sums are scaled by rsqrt(mean(x^2) + eps) from
+// ss_in (norm_w is not read).
 DRYFT_API int dryft_gemm_decode(const void* A, int lda, const void* W, void* C, int ldc, int mode, int M, int N,
                                 const float* norm_w, const float* ss_in, int ss_parts, float eps, float* ss_out, int pdl,
-                                cudaStream_t st) {
+                                int scaled, const float* next_w, void* xw_out, cudaStream_t st) {
   if (M <= 0 || N <= 0) return 0;
   if ((lda & 7) || M > 16) return DRYFT_ERR_UNSUPPORTED;
   if (((uintptr_t)A & 15) || ((uintptr_t)W & 15)) return DRYFT_ERR_UNSUPPORTED;
-  const bool norm = norm_w != nullptr;
-  if (norm && (!ss_in || ss_parts <= 0 || ((uintptr_t)norm_w & 15))) return DRYFT_ERR_UNSUPPORTED;
-  if (M <= 8) return launch1<1>(mode, norm, A, lda, W, C, ldc, M, N, norm_w, ss_in, ss_parts, eps, ss_out, pdl, st);
-  return launch1<2>(mode, norm, A, lda, W, C, ldc, M, N, norm_w, ss_in, ss_parts, eps, ss_out, pdl, st);
+  const int pro = scaled ? SCALED : (norm_w != nullptr ? NORMED : PLAIN);
+  if (pro != PLAIN && (!ss_in || ss_parts <= 0)) return DRYFT_ERR_UNSUPPORTED;
+  if (pro == NORMED && ((uintptr_t)norm_w & 15)) return DRYFT_ERR_UNSUPPORTED;
+  if ((xw_out != nullptr) != (next_w != nullptr) || (xw_out && mode != RESIDUAL)) return DRYFT_ERR_UNSUPPORTED;
+  Args a = {A, lda, W, C, ldc, M, N, norm_w, ss_in, ss_parts, eps, ss_out, next_w, xw_out, pdl, st};
+  return M <= 8 ? launch1<1>(mode, pro, a) : launch1<2>(mode, pro, a);
 }

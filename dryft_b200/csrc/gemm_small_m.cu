@@ -116,7 +116,7 @@ __global__ void __launch_bounds__(THREADS) gemm_small_m_kernel(
     if (tid < MP) {
       float s = 0.f;
       if (tid < M)
-        for (int p = 0; p < ss_parts; ++p) s += ss_in[p * SS_STRIDE + tid];
+        for (int p = 0; p < ss_parts; ++p) s += ld_prev(ss_in + p * SS_STRIDE + tid);
       inv_s[tid] = rsqrtf(s / (float)K + eps);
     }
     __syncthreads();
@@ -125,7 +125,7 @@ __global__ void __launch_bounds__(THREADS) gemm_small_m_kernel(
       const int m = i / chunks, c = i - m * chunks;
       uint4 out = zero;
       if (m < M) {
-        const uint4 raw = __ldg(reinterpret_cast<const uint4*>(A + (size_t)m * lda + c * 8));
+        const uint4 raw = ld_prev(reinterpret_cast<const uint4*>(A + (size_t)m * lda + c * 8));
         const float4 wv0 = __ldg(reinterpret_cast<const float4*>(norm_w + c * 8));
         const float4 wv1 = __ldg(reinterpret_cast<const float4*>(norm_w + c * 8 + 4));
         const float wv[8] = {wv0.x, wv0.y, wv0.z, wv0.w, wv1.x, wv1.y, wv1.z, wv1.w};
@@ -163,7 +163,7 @@ __global__ void __launch_bounds__(THREADS) gemm_small_m_kernel(
           uint4 a = zero;
           if (in) {
             if (NORM) a = *reinterpret_cast<const uint4*>(a_res + (size_t)m * KA + k);
-            else if (m < M) a = __ldg(reinterpret_cast<const uint4*>(A + (size_t)m * lda + k));
+            else if (m < M) a = ld_prev(reinterpret_cast<const uint4*>(A + (size_t)m * lda + k));
           }
           mma16816(acc[mb], wa[u].x, wb[u].x, wa[u].y, wb[u].y, a.x, a.y);
           mma16816(acc[mb], wa[u].z, wb[u].z, wa[u].w, wb[u].w, a.z, a.w);
@@ -209,7 +209,7 @@ __global__ void __launch_bounds__(THREADS) gemm_small_m_kernel(
         const int n = n0 + row;
         float sq = 0.f;
         if (m < M && n < N) {
-          const float v = bfr(__bfloat162float(x[(size_t)m * ldc + n]) + bfr(total(row, m)));
+          const float v = bfr(ld_prev_bf16(x + (size_t)m * ldc + n) + bfr(total(row, m)));
           x[(size_t)m * ldc + n] = __float2bfloat16_rn(v);
           sq = v * v;
         }
@@ -307,21 +307,24 @@ DRYFT_API int dryft_gemm_small_m(const void* A, int lda, const void* W, void* C,
 }
 
 // Sum of squares of each row of x [M, H] (bf16) -> ss[0][m]: the entry point of the chain of norm
-// prologues (the embedding's output has no product before it).
-__global__ void row_sumsq_kernel(const bf16* __restrict__ x, int hidden, float* __restrict__ ss) {
+// prologues (the embedding's output has no product before it).  With a norm weight w [H] it also leaves
+// the weighted activations xw = T(x * w) for a product that scales by the norm's factor in its epilogue.
+__global__ void row_sumsq_kernel(const bf16* __restrict__ x, int hidden, float* __restrict__ ss, const float* __restrict__ w,
+                                 bf16* __restrict__ xw) {
   __shared__ float scratch[33];
   const int m = blockIdx.x;
   float s = 0.f;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     const float v = __bfloat162float(x[(size_t)m * hidden + i]);
     s += v * v;
+    if (xw) xw[(size_t)m * hidden + i] = __float2bfloat16_rn(v * w[i]);
   }
   s = block_sum(s, scratch);
   if (threadIdx.x == 0) ss[m] = s;
 }
-DRYFT_API int dryft_row_sumsq(const void* x, int rows, int hidden, float* ss, cudaStream_t st) {
+DRYFT_API int dryft_row_sumsq(const void* x, int rows, int hidden, float* ss, const float* w, void* xw, cudaStream_t st) {
   if (rows <= 0) return 0;
-  if (rows > SS_STRIDE) return DRYFT_ERR_UNSUPPORTED;
-  row_sumsq_kernel<<<rows, 256, 0, st>>>((const bf16*)x, hidden, ss);
+  if (rows > SS_STRIDE || ((w != nullptr) != (xw != nullptr))) return DRYFT_ERR_UNSUPPORTED;
+  row_sumsq_kernel<<<rows, 256, 0, st>>>((const bf16*)x, hidden, ss, w, (bf16*)xw);
   return launch_status();
 }

@@ -262,7 +262,7 @@ __global__ void __launch_bounds__(THREADS) gemm_stream_kernel(const __grid_const
       for (int m = warp - 2; m < NB; m += 4) {
         float s = 0.f;
         if (m < p.M)
-          for (int i = lane; i < p.ss_parts; i += 32) s += p.ss_in[(size_t)i * SS_STRIDE + m];
+          for (int i = lane; i < p.ss_parts; i += 32) s += ld_prev(p.ss_in + (size_t)i * SS_STRIDE + m);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
         if (lane == 0) inv_s[m] = rsqrtf(s / (float)(p.n_kb * BK) + p.eps);
@@ -352,7 +352,7 @@ __global__ void __launch_bounds__(THREADS) gemm_stream_kernel(const __grid_const
           reinterpret_cast<bf16*>(p.C)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(sg * up);
         } else if (MODE == RESIDUAL) {
           bf16* x = reinterpret_cast<bf16*>(p.C);
-          const float v = bfr(__bfloat162float(x[(size_t)m * p.ldc + n]) + bfr(acc));
+          const float v = bfr(ld_prev_bf16(x + (size_t)m * p.ldc + n) + bfr(acc));
           x[(size_t)m * p.ldc + n] = __float2bfloat16_rn(v);
           sq = v * v;
         } else if (MODE == STORE_F32) {

@@ -67,14 +67,21 @@ class DecoderModel:
         packed rows ``want_rows`` (None if nothing is wanted).  ``all_rows`` says that ``want_rows`` is simply
         every row in order (a decode step), which lets the head take the fused path."""
         res = Residual(self.embedding.forward(ctx.tokens, ctx.n_tokens))
-        for i, st in enumerate(self.spec.schedule):
+        sched = self.spec.schedule
+        for i, st in enumerate(sched):
             block = self.blocks[st.layer]
-            res = block.forward(res, ctx, cache.entry(i), cache.state(i), owns_cache=st.cache_from is None)
+            if getattr(block, "takes_next_norm", False):
+                # the norm that reads the stream next: the following run step's first norm, or the final norm
+                nxt = getattr(self.blocks[sched[i + 1].layer], "norm_mixer", None) if i + 1 < len(sched) else self.final_norm
+                res = block.forward(res, ctx, cache.entry(i), cache.state(i), owns_cache=st.cache_from is None, next_norm=nxt)
+            else:
+                res = block.forward(res, ctx, cache.entry(i), cache.state(i), owns_cache=st.cache_from is None)
         if n_want == 0:
             return None
         if (all_rows and res.delta is None and res.ss is not None and hasattr(self.head, "forward_normed")
                 and self.head.can_fuse(res.x.shape[0], self.final_norm)):
-            return self.head.forward_normed(res.x, res.ss, res.ss_parts, self.final_norm)
+            xw = res.xw if res.xw_norm is self.final_norm else None
+            return self.head.forward_normed(res.x, res.ss, res.ss_parts, self.final_norm, **({"xw": xw} if xw is not None else {}))
         if res.delta is None:
             h = self.final_norm.forward(res.x, rows=want_rows, n_rows=n_want)
         else:

@@ -63,7 +63,7 @@ def core() -> ctypes.CDLL:
             lib.dryft_argmax_rows.argtypes = [_p, _i, _i, _ll, _p, _p, _p, _p]
             lib.dryft_sample_rows.argtypes = [_p, _i, _i, _ll, _f, _i, _ull, _p, _p, _i, _p, _p, _p, _p]
             lib.dryft_gemm_small_m.argtypes = [_p, _i, _p, _p, _i, _i, _i, _i, _i, _p, _p, _i, _f, _p, _i, _p]
-            lib.dryft_row_sumsq.argtypes = [_p, _i, _i, _p, _p]
+            lib.dryft_row_sumsq.argtypes = [_p, _i, _i, _p, _p, _p, _p]
             for name in ("dryft_step_meta", "dryft_step_advance", "dryft_tokens_from_state", "dryft_embed",
                          "dryft_rmsnorm", "dryft_residual_add", "dryft_silu_mul", "dryft_qk_norm_rope_store", "dryft_rope_table",
                          "dryft_gemm_nt_f32", "dryft_argmax_rows", "dryft_sample_rows", "dryft_gemm_small_m", "dryft_row_sumsq"):
@@ -104,7 +104,7 @@ def gemm_decode_lib(k: int) -> ctypes.CDLL:
         lib = _variants.get(key)
         if lib is None:
             lib = _load(build.build_library("gemm_decode", ("gemm_decode.cu",), {"DRYFT_K": k}))
-            lib.dryft_gemm_decode.argtypes = [_p, _i, _p, _p, _i, _i, _i, _i, _p, _p, _i, _f, _p, _i, _p]
+            lib.dryft_gemm_decode.argtypes = [_p, _i, _p, _p, _i, _i, _i, _i, _p, _p, _i, _f, _p, _i, _i, _p, _p, _p]
             lib.dryft_gemm_decode.restype = _i
             if lib.dryft_gemm_decode_k() != k:
                 raise KernelError("the compiled decode product is for another inner size")
@@ -569,8 +569,13 @@ SMALL_M_LIMIT = 16  # rows the weight-streaming product takes
 SS_STRIDE = 64  # floats per block in the sum-of-squares buffers of the fused decode products
 
 
+def weighted_ahead_supported(k: int) -> bool:
+    """Whether products over ``k`` inputs can take / leave activations weighted ahead (``xw_in`` / ``xw_out``)."""
+    return k > 0 and k % 256 == 0
+
+
 def gemm_small_m(a, w, out, *, mode: str = "store", norm_w=None, ss_in=None, ss_parts: int = 0, eps: float = 0.0,
-                 ss_out=None, pdl: bool = False) -> None:
+                 ss_out=None, pdl: bool = False, xw_in=None, next_w=None, xw_out=None) -> None:
     """``a[M,K] @ w[.,K].T`` for up to 16 rows (decode; K a multiple of 16): bfloat16 operands, 32-bit accumulation,
     every weight byte read once.  ``mode``:
 
@@ -583,9 +588,22 @@ def gemm_small_m(a, w, out, *, mode: str = "store", norm_w=None, ss_in=None, ss_
     With ``norm_w`` ``[K]`` float32 the rows of ``a`` are RMS-normalised on the fly; ``ss_in``
     ``[ss_parts, 64]`` holds their sums of squares as an earlier ``"residual"`` product (or ``row_sumsq``)
     left them.  ``pdl`` launches the kernel as a programmatic dependent of the launch before it: its
-    first weight requests overlap that launch's tail."""
+    first weight requests overlap that launch's tail.
+
+    The norm split over two launches (inner sizes that are multiples of 256 only, ``weighted_ahead_supported``):
+    a ``"residual"`` product given the next norm's weight ``next_w`` ``[N]`` also leaves ``xw_out[M,N] =
+    T(x * next_w)``; a product given such ``xw_in`` ``[M,K]`` (with ``ss_in``, ``eps``) multiplies it as plain
+    activations and scales its sums by the norm's factor in the epilogue -- no prologue on its critical path."""
     m, k = a.shape
     _need(a, "a", torch.bfloat16)
+    if xw_in is not None:
+        if not weighted_ahead_supported(k):
+            raise KernelError(f"gemm_small_m: activations weighted ahead need an inner size that is a multiple of 256, got {k}")
+        _need(xw_in, "xw_in", torch.bfloat16, (m, k))
+    if (next_w is None) != (xw_out is None):
+        raise KernelError("gemm_small_m: next_w and xw_out go together")
+    if xw_out is not None and (mode != "residual" or not weighted_ahead_supported(k)):
+        raise KernelError("gemm_small_m: xw_out belongs to mode='residual' with an inner size that is a multiple of 256")
     if mode == "silu":
         n = w.shape[0] // 2
         _need(w, "w", torch.bfloat16, (2 * n, k))
@@ -611,15 +629,28 @@ def gemm_small_m(a, w, out, *, mode: str = "store", norm_w=None, ss_in=None, ss_
         raise KernelError(f"gemm_small_m: unknown mode {mode!r}")
     if mode != "residual" and ss_out is not None:
         raise KernelError("gemm_small_m: ss_out belongs to mode='residual'")
-    if norm_w is not None:
-        _need(norm_w, "norm_w", torch.float32, (k,))
+    if norm_w is not None or xw_in is not None:
+        if norm_w is not None:
+            _need(norm_w, "norm_w", torch.float32, (k,))
         _need(ss_in, "ss_in", torch.float32)
         if ss_parts <= 0 or ss_in.numel() < ss_parts * SS_STRIDE:
             raise KernelError("gemm_small_m: ss_in does not hold ss_parts blocks")
+    if xw_out is not None:
+        _need(next_w, "next norm weight", torch.float32, (n,))
+        _need(xw_out, "xw_out", torch.bfloat16, (m, n))
     if k % 256 == 0:  # the form compiled for this inner size: loops unrolled, offsets immediate
-        rc = gemm_decode_lib(k).dryft_gemm_decode(_ptr(a), k, _ptr(w), _ptr(out), n, code, m, n, _ptr(norm_w), _ptr(ss_in),
-                                                  int(ss_parts), float(eps), _ptr(ss_out), int(pdl), _stream())
-        if rc != UNSUPPORTED:  # it refuses what does not fit its shared memory; the general form takes that
+        lib = gemm_decode_lib(k)
+        if xw_in is not None:
+            rc = lib.dryft_gemm_decode(_ptr(xw_in), k, _ptr(w), _ptr(out), n, code, m, n, None, _ptr(ss_in), int(ss_parts),
+                                       float(eps), _ptr(ss_out), int(pdl), 1, _ptr(next_w), _ptr(xw_out), _stream())
+            if rc != UNSUPPORTED:
+                _ok(rc, f"gemm_decode (M={m}, N={n}, K={k}, mode={mode}, activations weighted ahead)")
+                return
+            if norm_w is None:  # it refuses what does not fit its shared memory; with norm_w the plain form takes over
+                _ok(rc, f"gemm_decode (M={m}, N={n}, K={k}, mode={mode}, activations weighted ahead; give norm_w for the other form)")
+        rc = lib.dryft_gemm_decode(_ptr(a), k, _ptr(w), _ptr(out), n, code, m, n, _ptr(norm_w), _ptr(ss_in), int(ss_parts),
+                                   float(eps), _ptr(ss_out), int(pdl), 0, _ptr(next_w), _ptr(xw_out), _stream())
+        if rc != UNSUPPORTED or xw_out is not None:  # the general form below cannot leave xw_out
             _ok(rc, f"gemm_decode (M={m}, N={n}, K={k}, mode={mode})")
             return
     _ok(core().dryft_gemm_small_m(_ptr(a), k, _ptr(w), _ptr(out), n, code, m, n, k, _ptr(norm_w), _ptr(ss_in),
@@ -672,14 +703,20 @@ def gemm_stream(a, w, out, *, mode: str = "store", norm_w=None, ss_in=None, ss_p
         f"gemm_stream (M={m}, N={n}, K={k}, mode={mode})")
 
 
-def row_sumsq(x, ss) -> None:
-    """``ss[m] = sum(x[m]^2)`` for up to 64 rows of bfloat16 ``x``: one block of sums of squares."""
+def row_sumsq(x, ss, norm_w=None, xw_out=None) -> None:
+    """``ss[m] = sum(x[m]^2)`` for up to 64 rows of bfloat16 ``x``: one block of sums of squares.  With a norm
+    weight it also leaves ``xw_out = T(x * norm_w)`` for a product that takes activations weighted ahead."""
     rows, hidden = x.shape
     _need(x, "x", torch.bfloat16)
     _need(ss, "ss", torch.float32)
     if ss.numel() < SS_STRIDE:
         raise KernelError("row_sumsq: ss holds fewer than 64 floats")
-    _ok(core().dryft_row_sumsq(_ptr(x), rows, hidden, _ptr(ss), _stream()), "row_sumsq")
+    if (norm_w is None) != (xw_out is None):
+        raise KernelError("row_sumsq: norm_w and xw_out go together")
+    if xw_out is not None:
+        _need(norm_w, "norm weight", torch.float32, (hidden,))
+        _need(xw_out, "xw_out", torch.bfloat16, (rows, hidden))
+    _ok(core().dryft_row_sumsq(_ptr(x), rows, hidden, _ptr(ss), _ptr(norm_w), _ptr(xw_out), _stream()), "row_sumsq")
 
 
 # ----------------------------------------------------------------------------- token choice

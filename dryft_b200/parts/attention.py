@@ -23,7 +23,7 @@ from ..cache.store import CacheEntry, KVNeed, StateNeed
 from ..config.spec import PartSpec
 from ..ops import kernels as K
 from .base import NORMS, POSITIONS, Runtime, StepContext, TensorInfo, register_mixer
-from .linear import linear
+from .linear import linear, weighted_for
 
 PREFILL_TILE = 64      # query rows per block of the mma.sync prefill kernel
 PREFILL_TILE_TC = 128  # query rows per block of the tcgen05 prefill kernel
@@ -123,18 +123,31 @@ class Attention:
                 and type(norm).__name__ == "RMSNorm" and self.w_qkv.dtype == torch.bfloat16
                 and self.w_o.dtype == torch.bfloat16 and self.hidden % 16 == 0 and self.q_dim % 16 == 0)
 
-    def forward_normed(self, x, ss, ss_parts, norm, ctx, cache, state, owns_cache: bool = True):
+    weighted_ahead = True   # forward_normed takes ``xw`` / ``next_norm`` and returns the weighted stream too
+
+    def forward_normed(self, x, ss, ss_parts, norm, ctx, cache, state, owns_cache: bool = True, xw=None, next_norm=None):
         """``x += o_proj(attention(qkv_proj(norm(x))))`` in place: the norm inside the first product,
-        the add inside the last, which also leaves the new sums of squares of ``x``."""
+        the add inside the last, which also leaves the new sums of squares of ``x``.  ``xw``: ``x`` weighted
+        by ``norm``'s weight already (the first product then has no prologue).  ``next_norm``: the norm that
+        reads ``x`` next; the last product leaves ``x`` weighted for it where the sizes allow.
+        Returns ``(ss, ss_parts, xw or None)``."""
         n = x.shape[0]
         w = self.w_qkv if owns_cache else self.w_qkv[: self.q_dim]
         qkv = torch.empty((n, w.shape[0]), dtype=x.dtype, device=x.device)
-        K.gemm_small_m(x, w, qkv, norm_w=norm.weight, ss_in=ss, ss_parts=ss_parts, eps=norm.eps, pdl=self.rt.pdl)
+        if xw is not None and K.weighted_ahead_supported(self.hidden):
+            K.gemm_small_m(x, w, qkv, xw_in=xw, norm_w=norm.weight, ss_in=ss, ss_parts=ss_parts, eps=norm.eps, pdl=self.rt.pdl)
+        else:
+            K.gemm_small_m(x, w, qkv, norm_w=norm.weight, ss_in=ss, ss_parts=ss_parts, eps=norm.eps, pdl=self.rt.pdl)
         o = self._attend(qkv, ctx, cache, owns_cache)
         parts = (self.hidden + 15) // 16
         ss_out = torch.empty(parts * K.SS_STRIDE, dtype=torch.float32, device=x.device)
-        K.gemm_small_m(o, self.w_o, x, mode="residual", ss_out=ss_out, pdl=self.rt.pdl)
-        return ss_out, parts
+        xw_out = None
+        if weighted_for(next_norm, self.hidden, self.q_dim, self.rt):
+            xw_out = torch.empty_like(x)
+            K.gemm_small_m(o, self.w_o, x, mode="residual", ss_out=ss_out, pdl=self.rt.pdl, next_w=next_norm.weight, xw_out=xw_out)
+        else:
+            K.gemm_small_m(o, self.w_o, x, mode="residual", ss_out=ss_out, pdl=self.rt.pdl)
+        return ss_out, parts, xw_out
 
     def forward(self, h: torch.Tensor, ctx: StepContext, cache: CacheEntry, state, owns_cache: bool = True) -> torch.Tensor:
         if owns_cache:

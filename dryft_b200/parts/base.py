@@ -53,6 +53,7 @@ class Runtime:
     ffn_chunk_rows: int = 16384  # rows of the feed-forward processed at once (bounds [rows, 2I])
     fuse_decode: bool = True     # few rows: fold norms, residual adds and SiLU*mul into the products
     pdl: bool = True             # launch the fused decode products as programmatic dependents
+    norm_ahead: bool = True      # fused decode: a residual product leaves the stream weighted for the next norm
     tcgen05: bool = True         # prompts: attention on tcgen05.mma / tensor memory / TMA where sizes allow
 
     @property
@@ -91,6 +92,10 @@ class Residual:
     delta: Optional[torch.Tensor] = None
     ss: Optional[torch.Tensor] = None
     ss_parts: int = 0
+    # ``x`` already multiplied by the weight of the norm ``xw_norm`` (and rounded): left by a fused decode
+    # product for the product behind that norm, which then has no prologue (it scales its sums instead)
+    xw: Optional[torch.Tensor] = None
+    xw_norm: Optional[Any] = None
 
 
 class Registry:

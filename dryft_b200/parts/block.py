@@ -19,6 +19,7 @@ import torch
 
 from ..ops import kernels as K
 from .base import Residual, StepContext, register_block
+from .linear import weighted_for
 
 
 @register_block("prenorm")
@@ -34,22 +35,41 @@ class PreNormBlock:
         return (hasattr(m, "forward_normed") and hasattr(f, "forward_normed")
                 and m.can_fuse(n_rows, self.norm_mixer) and f.can_fuse(n_rows, self.norm_ffn))
 
-    def forward(self, res: Residual, ctx: StepContext, cache, state, owns_cache: bool = True) -> Residual:
+    takes_next_norm = True   # forward accepts the norm that will read the stream after this block
+
+    def forward(self, res: Residual, ctx: StepContext, cache, state, owns_cache: bool = True, next_norm=None) -> Residual:
         x = res.x
         if self._fusable(x.shape[0]):
             # few rows: five launches per layer.  Each product normalises / adds / activates on its own
-            # and hands the stream's sums of squares to the next one.
+            # and hands the stream's sums of squares (and, where sizes allow, the stream weighted for the
+            # next norm) to the next one.
             if res.delta is not None:
                 K.residual_add(x, res.delta)
                 res = Residual(x)
             ss, parts = res.ss, res.ss_parts
+            xw = res.xw if res.xw_norm is self.norm_mixer else None
+            ahead_m = getattr(self.mixer, "weighted_ahead", False)
+            ahead_f = getattr(self.ffn, "weighted_ahead", False)
             if ss is None:
                 ss = torch.empty(K.SS_STRIDE, dtype=torch.float32, device=x.device)
-                K.row_sumsq(x, ss)
+                if ahead_m and weighted_for(self.norm_mixer, x.shape[1], x.shape[1], self.mixer.rt):
+                    xw = torch.empty_like(x)
+                    K.row_sumsq(x, ss, norm_w=self.norm_mixer.weight, xw_out=xw)
+                else:
+                    K.row_sumsq(x, ss)
                 parts = 1
-            ss, parts = self.mixer.forward_normed(x, ss, parts, self.norm_mixer, ctx, cache, state, owns_cache)
-            ss, parts = self.ffn.forward_normed(x, ss, parts, self.norm_ffn, ctx)
-            return Residual(x, None, ss, parts)
+            if ahead_m:
+                ss, parts, xw = self.mixer.forward_normed(x, ss, parts, self.norm_mixer, ctx, cache, state, owns_cache,
+                                                          xw=xw, next_norm=self.norm_ffn if ahead_f else None)
+            else:
+                ss, parts = self.mixer.forward_normed(x, ss, parts, self.norm_mixer, ctx, cache, state, owns_cache)
+                xw = None
+            if ahead_f:
+                ss, parts, xw = self.ffn.forward_normed(x, ss, parts, self.norm_ffn, ctx, xw=xw, next_norm=next_norm)
+            else:
+                ss, parts = self.ffn.forward_normed(x, ss, parts, self.norm_ffn, ctx)
+                xw = None
+            return Residual(x, None, ss, parts, xw, next_norm if xw is not None else None)
         h = self.norm_mixer.forward(x) if res.delta is None else self.norm_mixer.add_forward(x, res.delta)
         a = self.mixer.forward(h, ctx, cache, state, owns_cache)
         h = self.norm_ffn.add_forward(x, a)

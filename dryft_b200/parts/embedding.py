@@ -72,8 +72,12 @@ class LMHead:
                 and type(norm).__name__ == "RMSNorm" and self.weight.dtype == torch.bfloat16
                 and self.weight.shape[1] % 16 == 0)
 
-    def forward_normed(self, x: torch.Tensor, ss, ss_parts: int, norm) -> torch.Tensor:
-        """Logits of every row of ``x`` with the final norm inside the product (decode)."""
+    def forward_normed(self, x: torch.Tensor, ss, ss_parts: int, norm, xw=None) -> torch.Tensor:
+        """Logits of every row of ``x`` with the final norm inside the product (decode); ``xw``: ``x``
+        weighted by the final norm's weight already."""
         out = torch.empty((x.shape[0], self.vocab), dtype=torch.float32, device=x.device)
-        K.gemm_small_m(x, self.weight, out, norm_w=norm.weight, ss_in=ss, ss_parts=ss_parts, eps=norm.eps, pdl=self.rt.pdl)
+        if xw is not None and K.weighted_ahead_supported(x.shape[1]):
+            K.gemm_small_m(x, self.weight, out, xw_in=xw, norm_w=norm.weight, ss_in=ss, ss_parts=ss_parts, eps=norm.eps, pdl=self.rt.pdl)
+        else:
+            K.gemm_small_m(x, self.weight, out, norm_w=norm.weight, ss_in=ss, ss_parts=ss_parts, eps=norm.eps, pdl=self.rt.pdl)
         return out

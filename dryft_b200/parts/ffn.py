@@ -12,7 +12,7 @@ import torch
 
 from ..ops import kernels as K
 from .base import Runtime, StepContext, TensorInfo, register_ffn
-from .linear import linear
+from .linear import linear, weighted_for
 
 
 @register_ffn("swiglu")
@@ -40,17 +40,28 @@ class SwiGLU:
                 and type(norm).__name__ == "RMSNorm" and self.w_gate_up.dtype == torch.bfloat16
                 and self.w_down.dtype == torch.bfloat16 and self.hidden % 16 == 0 and self.inter % 16 == 0)
 
-    def forward_normed(self, x, ss, ss_parts, norm, ctx):
+    weighted_ahead = True   # forward_normed takes ``xw`` / ``next_norm`` and returns the weighted stream too
+
+    def forward_normed(self, x, ss, ss_parts, norm, ctx, xw=None, next_norm=None):
         """``x += down(silu(gate(norm(x))) * up(norm(x)))`` in place, two launches: the norm and the
-        SiLU*mul inside the first product, the add (and the new sums of squares) inside the second."""
+        SiLU*mul inside the first product, the add (and the new sums of squares) inside the second.
+        ``xw`` / ``next_norm`` as in the attention mixer.  Returns ``(ss, ss_parts, xw or None)``."""
         n = x.shape[0]
         act = torch.empty((n, self.inter), dtype=x.dtype, device=x.device)
-        K.gemm_small_m(x, self.w_gate_up, act, mode="silu", norm_w=norm.weight, ss_in=ss, ss_parts=ss_parts,
-                       eps=norm.eps, pdl=self.rt.pdl)
+        if xw is not None and K.weighted_ahead_supported(self.hidden):
+            K.gemm_small_m(x, self.w_gate_up, act, mode="silu", xw_in=xw, norm_w=norm.weight, ss_in=ss, ss_parts=ss_parts, eps=norm.eps, pdl=self.rt.pdl)
+        else:
+            K.gemm_small_m(x, self.w_gate_up, act, mode="silu", norm_w=norm.weight, ss_in=ss, ss_parts=ss_parts,
+                           eps=norm.eps, pdl=self.rt.pdl)
         parts = (self.hidden + 15) // 16
         ss_out = torch.empty(parts * K.SS_STRIDE, dtype=torch.float32, device=x.device)
-        K.gemm_small_m(act, self.w_down, x, mode="residual", ss_out=ss_out, pdl=self.rt.pdl)
-        return ss_out, parts
+        xw_out = None
+        if weighted_for(next_norm, self.hidden, self.inter, self.rt):
+            xw_out = torch.empty_like(x)
+            K.gemm_small_m(act, self.w_down, x, mode="residual", ss_out=ss_out, pdl=self.rt.pdl, next_w=next_norm.weight, xw_out=xw_out)
+        else:
+            K.gemm_small_m(act, self.w_down, x, mode="residual", ss_out=ss_out, pdl=self.rt.pdl)
+        return ss_out, parts, xw_out
 
     def _rows(self, h: torch.Tensor) -> torch.Tensor:
         gu = linear(h, self.w_gate_up, self.rt)

@@ -30,8 +30,13 @@ TINY: Dict[str, dict] = {
               intermediate_size=176, vocab_size=331, rope_theta=500000.0, rms_norm_eps=3e-6,
               tie_word_embeddings=False, max_position_embeddings=2048,
               use_sliding_window=True, sliding_window=40, max_window_layers=1),
+    # widths that are multiples of 256: the decode products compiled per inner size and the norm split
+    # over two launches only run at such widths (hidden 256, q width 512, intermediate 512)
+    "d": dict(num_hidden_layers=3, hidden_size=256, num_attention_heads=8, num_key_value_heads=2, head_dim=64,
+              intermediate_size=512, vocab_size=300, rope_theta=10000.0, rms_norm_eps=1e-6,
+              tie_word_embeddings=False, max_position_embeddings=512),
 }
-SEEDS = {"a": 0, "b": 1, "c": 2}
+SEEDS = {"a": 0, "b": 1, "c": 2, "d": 3}
 # normal(0, 0.02) weights give nearly flat logits on models this small; a wider spread makes every
 # stage matter (the reference multiplies its tiny model's weights by 4, agent/verify.py:49-51)
 STD = 0.08

@@ -191,6 +191,25 @@ def test_gemm_small_m_fused_norm_residual_silu(m, n, k_):
         k.gemm_small_m(res, w2, out2, norm_w=nw2, ss_in=ss_out, ss_parts=parts, eps=eps)
         ref2 = P.rmsnorm(res.cpu(), nw2.cpu(), eps).double() @ w2.cpu().double().T
         torch.testing.assert_close(out2.cpu().double(), ref2, rtol=2e-2, atol=2e-2)
+    # the norm split over two launches: the residual product leaves the new stream weighted for the next
+    # norm, and a second product scales its sums by the norm's factor instead of normalising its input
+    if k.weighted_ahead_supported(k_) and k.weighted_ahead_supported(n):
+        res3 = res0.clone()
+        nw2 = (1 + 0.1 * torch.randn(n, device=DEV)).to(bf).float()
+        xw = torch.full((m, n), 7.0, device=DEV, dtype=bf)
+        ss3 = torch.full((parts * 64,), -1.0, device=DEV)
+        k.gemm_small_m(x, w, res3, mode="residual", ss_out=ss3, next_w=nw2, xw_out=xw)
+        assert torch.equal(res3, res)
+        assert torch.equal(xw.cpu(), (res.float().cpu() * nw2.cpu()).to(bf))
+        w2 = (torch.randn(48, n, device=DEV) / math.sqrt(n)).to(bf)
+        out3 = torch.empty(m, 48, device=DEV, dtype=torch.float32)
+        k.gemm_small_m(res, w2, out3, xw_in=xw, norm_w=nw2, ss_in=ss3, ss_parts=parts, eps=eps)   # norm_w: for sizes the split form refuses
+        ref3 = P.rmsnorm(res.cpu(), nw2.cpu(), eps).double() @ w2.cpu().double().T
+        torch.testing.assert_close(out3.cpu().double(), ref3, rtol=2e-2, atol=2e-2)
+        act3 = torch.empty(m, 24, device=DEV, dtype=bf)
+        k.gemm_small_m(res, w2, act3, mode="silu", xw_in=xw, norm_w=nw2, ss_in=ss3, ss_parts=parts, eps=eps)
+        gu3 = P.matmul_nt(P.rmsnorm(res.cpu(), nw2.cpu(), eps), w2.cpu(), bf)
+        torch.testing.assert_close(act3.cpu().float(), P.silu_mul(gu3[:, :24], gu3[:, 24:]).float(), rtol=3e-2, atol=3e-2)
     # SiLU*mul epilogue over gate rows then up rows
     inter = n // 2
     act = torch.empty(m, inter, device=DEV, dtype=bf)

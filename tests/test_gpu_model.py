@@ -15,7 +15,7 @@ import plain_qwen3 as P
 pytestmark = pytest.mark.gpu
 
 DTYPES = [torch.float32, torch.bfloat16]
-NAMES = ["a", "b", "c"]
+NAMES = ["a", "b", "c", "d"]
 
 _engines = {}
 _plains = {}
@@ -281,6 +281,35 @@ def test_fused_decode_products_equal_the_separate_kernels(model_dirs):
     p32 = plain_for(model_dirs, "b", torch.float32).logits(toks)[29:]
     pb = plain_for(model_dirs, "b", torch.bfloat16).logits(toks)[29:]
     assert H.rel_err(outs[0], outs[2]) <= H.bf16_tol(pb, p32)
+    from dryft_b200.ops import kernels as K
+    K.check_error_flags()
+
+
+def test_norm_split_over_two_launches(model_dirs):
+    """At widths that are multiples of 256 a fused decode product leaves the stream weighted for the next
+    norm and the product behind that norm scales its sums instead of normalising its input.  Decoding token
+    by token must stay within bfloat16 rounding of the plain implementation and of the same engine with the
+    split switched off; CUDA-graph decoding must give the same tokens as eager decoding."""
+    on = engine_for(model_dirs, "d", torch.bfloat16)
+    off = engine_for(model_dirs, "d", torch.bfloat16, norm_ahead=False)
+    toks = H.prompts_for("d", [60], seed=21)[0]
+    outs = []
+    for eng in (on, off):
+        s = eng.cache.open_sequences(1)
+        rows = [step(eng, s, [toks[:28]], [[27]])]
+        for t in toks[28:]:
+            rows.append(step(eng, s, [[t]], [[0]]))
+        eng.cache.close_sequences(s)
+        outs.append(torch.cat(rows).float().cpu())
+    p32 = plain_for(model_dirs, "d", torch.float32).logits(toks)[27:]
+    pb = plain_for(model_dirs, "d", torch.bfloat16).logits(toks)[27:]
+    tol = H.bf16_tol(pb, p32)
+    assert not torch.equal(outs[0], outs[1]), "the split path did not run"
+    assert H.rel_err(outs[0], pb) <= tol and H.rel_err(outs[1], pb) <= tol
+    assert H.rel_err(outs[0], outs[1]) <= tol
+    prompts = H.prompts_for("d", [9, 2, 40], seed=8)
+    eager = engine_for(model_dirs, "d", torch.bfloat16, cuda_graphs=False)
+    assert [s for s in on.generate(prompts, 16)] == [s for s in eager.generate(prompts, 16)]
     from dryft_b200.ops import kernels as K
     K.check_error_flags()
 
