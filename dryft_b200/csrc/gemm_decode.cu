@@ -153,7 +153,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
     constexpr int CHUNKS = K / 8;
     constexpr int ITEMS = MP * CHUNKS;
     constexpr int PER = ITEMS / THREADS;
-    constexpr int BATCH = PER <= 5 ? PER : 5;
+    constexpr int BATCH = PER <= 10 ? PER : 10;   // one trip for eight rows of up to 2,560
 #pragma unroll 1
     for (int first = 0; first < PER; first += BATCH) {
       uint4 raw[BATCH];
