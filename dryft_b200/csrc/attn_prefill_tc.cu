@@ -336,6 +336,8 @@ __global__ void __launch_bounds__(THREADS, 2) attn_prefill_tc_kernel(
         alpha = m_new == -INFINITY ? 1.f : fast_exp2(m_run - m_new);
         m_run = m_new;
         if (j > 0) {
+          // S of tile j is done, hence every product issued before it, the P V of tile j-2 among them: the
+          // barrier is in phase j-1 or j, which one parity bit tells apart
           ok = mbar_wait(o_done, (unsigned)((j - 1) & 1), err, failed);   // O holds tiles 0 .. j-1
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
@@ -366,6 +368,13 @@ __global__ void __launch_bounds__(THREADS, 2) attn_prefill_tc_kernel(
       l_run = l_run * alpha + sum;
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       mbar_arrive(&p_ready[j & 1]);
+    }
+    if (ok && n_tiles >= 2) {
+      // A parity wait tells two phases apart, not three.  This thread last saw S of the last tile, which
+      // only proves the P V product of tile n-3 done; the one of tile n-2 was issued after that S.  So
+      // first the phase of tile n-2 (else, were it still running, its parity would pass for "n-1 done")
+      ok = mbar_wait(o_done, (unsigned)((n_tiles - 2) & 1), err, failed);
+      ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {
       ok = mbar_wait(o_done, (unsigned)((n_tiles - 1) & 1), err, failed);

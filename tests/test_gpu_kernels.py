@@ -668,6 +668,43 @@ def test_attn_prefill_tc_running_maximum(where):
     torch.testing.assert_close(out.cpu().float(), ref, rtol=2e-2, atol=2e-2)
 
 
+def test_attn_prefill_tc_is_the_same_every_time():
+    """Many blocks, many launches, one input, L2 flushed every other launch so that K and V arrive late:
+    every launch must give the same bits.  (A block once read its accumulator after a wait that one parity
+    bit could not decide -- the P V product of the tile before the last still running -- about one prompt
+    step in forty; nothing in the kernel may depend on when its copies and products finish.)"""
+    k = K()
+    dtype = torch.bfloat16
+    n_heads, n_kv, d, page, tile = 16, 4, 128, 64, 128
+    scale = 1.0 / math.sqrt(d)
+    lens = [70, 250, 129, 5, 200, 128, 33, 90, 64, 17, 31, 3]
+    seqs = {i: (torch.randn(L, n_kv, d).to(dtype), torch.randn(L, n_kv, d).to(dtype)) for i, L in enumerate(lens)}
+    kc, vc, pt = _fill_cache(seqs, n_kv, d, page, dtype, n_pages=40, max_pages=4, slots=len(lens), scatter_seed=9)
+    tok_slot, tok_pos, tiles0, tilesn = [], [], [], []
+    base = 0
+    for i, L in enumerate(lens):
+        tok_slot += [i] * L
+        tok_pos += list(range(L))
+        for q0 in range(0, L, tile):
+            tiles0.append(base + q0)
+            tilesn.append(min(tile, L - q0))
+        base += L
+    q = torch.randn(base, n_heads, d, device=DEV).to(dtype)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    args = (q, kc, vc, pt, i32(tiles0), i32(tilesn), i32(tok_slot), i32(tok_pos))
+    first = torch.empty(base, n_heads * d, device=DEV, dtype=dtype)
+    k.attn_prefill_tc(*args, first, len(tiles0), scale, None)
+    out = torch.empty_like(first)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=DEV)   # larger than L2: the next launch's K and V come late
+    for it in range(120):
+        if it % 2:
+            flush.fill_(it & 255)
+        k.attn_prefill_tc(*args, out, len(tiles0), scale, None)
+        assert torch.equal(out, first), f"launch {it} differs"
+    torch.cuda.synchronize()
+    k.check_error_flags()
+
+
 # ------------------------------------------------------------------------------------ token choice
 def test_argmax_rows_ties_and_state():
     k = K()

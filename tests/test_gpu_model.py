@@ -717,19 +717,21 @@ def test_toy_routed_ffn_and_toy_position_encoding_register_build_and_step():
 
 
 @pytest.mark.gpu
-def test_decode_at_production_widths_is_the_same_with_and_without_launch_overlap():
+@pytest.mark.parametrize("n_seqs", [8, 12])
+def test_decode_at_production_widths_is_the_same_with_and_without_launch_overlap(n_seqs):
     """Two layers at the widths the benchmark runs (hidden 2560, q width 4096, intermediate 9728): the
-    fused decode step captured in a CUDA graph, whose launches overlap as programmatic dependents, must
-    give bit for bit the logits of the same kernels launched one after the other; and stay within bfloat16
-    rounding of the separate-kernel path, measured against the 32-bit engine on the same weights."""
+    decode step captured in a CUDA graph, whose launches overlap as programmatic dependents, must give bit
+    for bit the logits of the same kernels launched one after the other; and stay within bfloat16 rounding
+    of the separate-kernel path, measured against the 32-bit engine on the same weights.  Eight sequences
+    take the fused products; twelve take the library products with the one-launch attention between them."""
     from dryft_b200.config import preset
     from dryft_b200.engine.api import Engine
 
     raw = dict(preset("qwen3-4b"))
     raw.update(num_hidden_layers=2, vocab_size=8192, max_position_embeddings=2048)
-    kw = dict(seed=4, std=0.03, max_batch=8, max_seq_len=1024, max_tokens=8 * 1024)
+    kw = dict(seed=4, std=0.03, max_batch=16, max_seq_len=1024, max_tokens=16 * 1024)
     g = torch.Generator().manual_seed(5)
-    prompts = [torch.randint(0, 8192, (n,), generator=g).tolist() for n in (70, 3, 129, 64, 200, 17, 31, 90)]
+    prompts = [torch.randint(0, 8192, (n,), generator=g).tolist() for n in (70, 3, 129, 64, 200, 17, 31, 90, 5, 250, 33, 128)[:n_seqs]]
 
     def decode_logits(**opts):
         eng = Engine.from_config(raw, **kw, **opts)
