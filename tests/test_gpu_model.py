@@ -759,3 +759,45 @@ def test_decode_at_production_widths_is_the_same_with_and_without_launch_overlap
     exact = decode_logits(dtype="float32")
     tol = H.bf16_tol(separate, exact)
     assert H.rel_err(overlapped, separate) <= tol and H.rel_err(overlapped, exact) <= tol
+
+
+@pytest.mark.gpu
+def test_same_requests_give_the_same_logits_every_time_at_production_widths():
+    """One engine, the same twelve prompts prefilled and decoded twenty times over (slots and pages are
+    given back and taken again in between, L2 flushed every other time): prompt logits and decode logits
+    must be the same bits every time.  Nothing may depend on when a copy, a product or a launch finishes."""
+    from dryft_b200.config import preset
+    from dryft_b200.engine.api import Engine
+
+    raw = dict(preset("qwen3-4b"))
+    raw.update(num_hidden_layers=2, vocab_size=8192, max_position_embeddings=2048)
+    g = torch.Generator().manual_seed(6)
+    prompts = [torch.randint(0, 8192, (n,), generator=g).tolist() for n in (70, 3, 129, 64, 200, 17, 31, 90, 5, 250, 33, 128)]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for n_seqs in (8, 12):   # the fused decode products; the library products with the one-launch attention
+        eng = Engine.from_config(raw, seed=4, std=0.03, dtype="bfloat16", max_batch=16, max_seq_len=1024, max_tokens=16 * 1024)
+        first = None
+        for rep in range(20):
+            if rep % 2:
+                flush.fill_(rep)
+            outs = []
+            with torch.inference_mode():
+                s = eng.cache.open_sequences(n_seqs)
+                lg = eng.stepper.step(s, prompts[:n_seqs], [[len(p) - 1] for p in prompts[:n_seqs]])
+                outs.append(lg.float().cpu())
+                idx = torch.tensor(s, device="cuda")
+                eng.cache.last_token[idx] = lg.argmax(-1).int()
+                for _ in range(4):
+                    lg = eng.stepper.decode_from_state(s)[:n_seqs].float()
+                    outs.append(lg.cpu())
+                    eng.cache.last_token[idx] = lg.argmax(-1).int()
+                eng.cache.close_sequences(s)
+            got = torch.stack(outs)
+            if first is None:
+                first = got
+            else:
+                assert torch.equal(got, first), f"{n_seqs} sequences, repetition {rep}: logits differ from the first time"
+        del eng
+        torch.cuda.empty_cache()
+    from dryft_b200.ops import kernels as K
+    K.check_error_flags()
