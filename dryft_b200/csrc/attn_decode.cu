@@ -330,19 +330,33 @@ __global__ void __launch_bounds__(NWARP * 32) attn_decode_kernel(const Params p)
     }
 
     // S = Q K^T: 16 (heads, padded) x 16 keys
-    float s[2][4];
+    // the k steps go round NCH accumulators per key half: chains of dependent products NCH times shorter
+    constexpr int NCH = KSTEPS >= 2 ? 2 : 1;   // four chains measured no better than two
+    float sp[NCH][2][4];
 #pragma unroll
-    for (int j = 0; j < 2; ++j)
+    for (int c = 0; c < NCH; ++c)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) s[j][i] = 0.f;
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) sp[c][j][i] = 0.f;
 #pragma unroll
     for (int kk = 0; kk < KSTEPS; ++kk) {
       unsigned a0, a1, a2, a3, b0, b1, b2, b3;
       ldsm_x4(a0, a1, a2, a3, qs + (lane & 15) * KS + kk * 16 + (lane >> 4) * 8);
       ldsm_x4(b0, b1, b2, b3, kst + ((lane & 7) + (lane >> 4) * 8) * KS + kk * 16 + ((lane >> 3) & 1) * 8);
-      mma16816(s[0], a0, a1, a2, a3, b0, b1);
-      mma16816(s[1], a0, a1, a2, a3, b2, b3);
+      mma16816(sp[kk % NCH][0], a0, a1, a2, a3, b0, b1);
+      mma16816(sp[kk % NCH][1], a0, a1, a2, a3, b2, b3);
     }
+    float s[2][4];
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float t = sp[0][j][i];
+#pragma unroll
+        for (int c = 1; c < NCH; ++c) t += sp[c][j][i];
+        s[j][i] = t;
+      }
     // mask, online softmax (log2 domain); every slice visited holds at least one visible key
     const int key0 = sl * SLICE;
     float mx0 = -INFINITY, mx1 = -INFINITY;
