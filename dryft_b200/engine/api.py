@@ -157,6 +157,8 @@ class _DeviceBackend:
         self.d2h_bytes = 0
         self._seq_key = None
         self._seq_dev = None
+        self._ring = None      # pinned buffers for the chosen tokens of the steps in flight
+        self._ring_at = 0
 
     def open(self, n: int) -> List[int]:
         return self.e.cache.open_sequences(n)
@@ -180,6 +182,11 @@ class _DeviceBackend:
         return chosen.tolist()
 
     def decode(self, handles, seq_ids, step: int, params: SamplingParams) -> List[int]:
+        return self.decode_result(self.decode_launch(handles, seq_ids, step, params))
+
+    def decode_launch(self, handles, seq_ids, step: int, params: SamplingParams):
+        """Start a decode step: the graph, the token choice and the copy of the chosen tokens into pinned
+        memory are queued; nothing waits.  The ticket is redeemed by ``decode_result``."""
         e = self.e
         n = len(handles)
         logits = e.stepper.decode_from_state(handles)
@@ -195,4 +202,17 @@ class _DeviceBackend:
                         last_token=e.cache.last_token)
         self.h2d_bytes += 4 * bucket  # the step's slot list, staged in pinned memory
         self.d2h_bytes += 4 * n
-        return chosen[:n].tolist()
+        if self._ring is None or self._ring[0].numel() < bucket:
+            self._ring = [torch.empty(max(bucket, 64), dtype=torch.int32).pin_memory() for _ in range(4)]
+            self._ring_at = 0
+        host = self._ring[self._ring_at]
+        self._ring_at = (self._ring_at + 1) % len(self._ring)
+        host[:n].copy_(chosen[:n], non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+        return host, n, done
+
+    def decode_result(self, ticket) -> List[int]:
+        host, n, done = ticket
+        done.synchronize()
+        return host[:n].tolist()

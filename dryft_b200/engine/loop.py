@@ -6,7 +6,10 @@ backend.  The shape of the API follows ``engine/engine.py:138-166,192-234`` of h
 the first from the prompts' step.  Differences, on purpose: prompts of unequal lengths run in ONE
 step (the reference groups them by length, ``engine.py:172-186``); a sequence may stop early at a
 stop token (the reference never stops, ``engine.py:139-140``) — it is then left out of later steps
-and its entry in later yields is -1; the loop ends when every sequence has ended.
+and its entry in later yields is -1; the loop ends when every sequence has ended.  Without stop tokens
+the host need not see step t's tokens before step t+1 runs (the tokens stay on the device), so a backend
+that offers ``decode_launch`` / ``decode_result`` keeps one step in flight: step t+1 is launched before
+step t's tokens are read, as the reference does with its pinned ring (``engine.py:215-229``).
 """
 
 from __future__ import annotations
@@ -26,6 +29,8 @@ class Backend(Protocol):
                 params: SamplingParams) -> List[int]: ...
     def decode(self, handles: Sequence[int], seq_ids: Sequence[int], step: int, params: SamplingParams) -> List[int]: ...
     def close(self, handles: Sequence[int]) -> None: ...
+    # optional pair: ``decode_launch(handles, seq_ids, step, params) -> ticket`` starts a decode step without
+    # waiting for it, ``decode_result(ticket) -> List[int]`` waits for that step and returns its tokens
 
 
 def check_request(input_ids: Sequence[Sequence[int]], max_new_tokens: int) -> None:
@@ -53,6 +58,17 @@ def run_batch(backend: Backend, prompts: Sequence[Sequence[int]], max_new_tokens
         alive = list(range(B))
         toks = backend.prefill(handles, prompts, seq_ids, params)
         step = 0
+        if not stops and hasattr(backend, "decode_launch") and hasattr(backend, "decode_result"):
+            # nobody can end early: every step runs all sequences, and one step is kept in flight
+            yield [int(t) for t in toks]          # the first tokens go out before any decode step is launched
+            if max_new_tokens == 1:
+                return
+            ticket = backend.decode_launch(handles, seq_ids, 1, params)
+            for step in range(1, max_new_tokens):
+                ahead = backend.decode_launch(handles, seq_ids, step + 1, params) if step + 1 < max_new_tokens else None
+                yield [int(t) for t in backend.decode_result(ticket)]
+                ticket = ahead
+            return
         while True:
             out = [ENDED] * B
             for b, t in zip(alive, toks):

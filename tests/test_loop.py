@@ -136,3 +136,49 @@ def test_sampling_params_are_validated():
     with pytest.raises(ValueError):
         SamplingParams(top_k=-2)
     assert SamplingParams().greedy and not SamplingParams(temperature=0.7).greedy
+
+
+class ScriptedInFlight(Scripted):
+    """The same backend with the optional pair: a step is launched, and its tokens are fetched later."""
+
+    def decode_launch(self, handles, seq_ids, step, params):
+        self.calls.append(("launch", step))
+        return (step, self.decode(handles, seq_ids, step, params))
+
+    def decode_result(self, ticket):
+        step, toks = ticket
+        self.calls.append(("result", step))
+        return toks
+
+
+def test_one_step_is_kept_in_flight_when_nothing_can_stop_early():
+    script = {0: [10, 11, 12, 13], 1: [20, 21, 22, 23]}
+    plain = list(run_batch(Scripted(script), [[1, 2, 3], [4]], 4, GREEDY))
+    be = ScriptedInFlight(script)
+    seen = []
+    for out in run_batch(be, [[1, 2, 3], [4]], 4, GREEDY):
+        seen.append((out, [c for c in be.calls if c[0] in ("launch", "result")]))
+    assert [o for o, _ in seen] == plain == [[10, 20], [11, 21], [12, 22], [13, 23]]
+    assert seen[0][1] == []                                          # the first tokens go out before any decode step is launched
+    order = [c for c in be.calls if c[0] in ("launch", "result")]
+    assert order == [("launch", 1), ("launch", 2), ("result", 1), ("launch", 3), ("result", 2), ("result", 3)]
+    assert be.calls[-1][0] == "close" and sorted(be.free) == list(range(8))
+    # a single new token: no decode step at all
+    be = ScriptedInFlight(script)
+    assert list(run_batch(be, [[1], [2]], 1, GREEDY)) == [[10, 20]] and not [c for c in be.calls if c[0] == "launch"]
+
+
+def test_stop_tokens_switch_the_flight_off():
+    """With stop tokens the host must see a step's tokens before it can decide who runs the next one."""
+    be = ScriptedInFlight({0: [10, 99, 12], 1: [20, 21, 22]})
+    out = list(run_batch(be, [[1], [2]], 3, GREEDY, stop_token_ids=[99]))
+    assert out == [[10, 20], [99, 21], [ENDED, 22]]
+    assert not [c for c in be.calls if c[0] in ("launch", "result")]
+
+
+def test_leaving_early_with_a_step_in_flight_gives_the_slots_back():
+    be = ScriptedInFlight({0: [10, 11, 12, 13], 1: [20, 21, 22, 23]})
+    gen = run_batch(be, [[1], [2]], 4, GREEDY)
+    assert next(gen) == [10, 20] and next(gen) == [11, 21]
+    gen.close()
+    assert be.calls[-1][0] == "close" and sorted(be.free) == list(range(8))
