@@ -21,7 +21,7 @@ head) with random weights, a batch of 8 sequences with 512-token prompts, and ti
 The method follows hari495/dryft's ``agent/bench.py:96-126`` (warm-up, synchronize on both sides,
 seeded uniform token ids, ``bench.py:111-119``); its achieved-bandwidth figure (``bench.py:171-172``) is
 the ``roofline`` entry.  The reference arm is unavailable: hari495/dryft has neither setup.py nor
-pyproject.toml, so ``pip install --no-index ... /root/reference`` refuses it.
+pyproject.toml, so ``pip install --no-index ... <its checkout>`` refuses it.
 """
 
 import argparse
@@ -194,7 +194,7 @@ def main() -> int:
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable": "hari495/dryft has no setup.py or pyproject.toml; pip install "
-                          "--no-index --target baseline/_ref /root/reference fails with 'Directory is not installable'"}))
+                          "--no-index --target baseline/_ref <reference checkout> fails with 'Directory is not installable'"}))
         return 0
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not measured")

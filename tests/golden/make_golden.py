@@ -1,7 +1,7 @@
 """Makes ``tests/golden/*.safetensors``: logits of hari495/dryft's OWN model code on the CPU, for
 the plain implementation (``tests/plain_qwen3.py``) to be compared with once.
 
-    python tests/golden/make_golden.py [/path/to/hari495-dryft]      (default: $DRYFT_REFERENCE or /root/reference)
+    python tests/golden/make_golden.py [/path/to/hari495-dryft]      (default: $DRYFT_REFERENCE)
 
 How the reference is driven (nothing in its tree is changed):
   * ``dryft_qwen3.config.EXPECTED_CONFIG = None`` lifts the pin to one checkpoint
@@ -118,7 +118,9 @@ def run_case(ref_root: str, case: dict, dtype: torch.dtype):
 
 
 def main() -> int:
-    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("DRYFT_REFERENCE", "/root/reference")
+    ref = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("DRYFT_REFERENCE", "")
+    if not ref:
+        raise SystemExit("give the path of a checkout of hari495/dryft (argument or $DRYFT_REFERENCE)")
     if not os.path.isdir(os.path.join(ref, "engine", "dryft_qwen3")):
         print(f"reference not found at {ref}", file=sys.stderr)
         return 1
