@@ -75,12 +75,12 @@ __device__ __forceinline__ bool mbar_try_wait(void* bar, unsigned parity) {
                : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
   return ok != 0;
 }
-__device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity, int* err, volatile int* failed) {
+__device__ __forceinline__ bool mbar_wait(void* bar, unsigned parity, int* err, volatile int* failed, int site = 1) {
   const long long t0 = clock64();
   while (!mbar_try_wait(bar, parity)) {
     if (*failed) return false;
     if (clock64() - t0 > WAIT_CYCLES) {
-      if (err) atomicExch(err, 1);
+      if (err) atomicCAS(err, 0, site);   // the first wait that gave up names its place
       *failed = 1;
       return false;
     }
@@ -234,11 +234,11 @@ __global__ void __launch_bounds__(THREADS, 2) attn_prefill_tc_kernel(
       bool ok = true;
       for (int j = 0; j < n_tiles && ok; ++j) {
         if (j + 1 < n_tiles) {
-          if (j + 1 >= STAGES) ok = mbar_wait(&k_free[(j + 1) % STAGES], (unsigned)((((j + 1) / STAGES) - 1) & 1), err, failed);
+          if (j + 1 >= STAGES) ok = mbar_wait(&k_free[(j + 1) % STAGES], (unsigned)((((j + 1) / STAGES) - 1) & 1), err, failed, 2);
           if (!ok) break;
           load_k(j + 1);
         }
-        if (j >= STAGES) ok = mbar_wait(&v_free[j % STAGES], (unsigned)(((j / STAGES) - 1) & 1), err, failed);
+        if (j >= STAGES) ok = mbar_wait(&v_free[j % STAGES], (unsigned)(((j / STAGES) - 1) & 1), err, failed, 3);
         if (!ok) break;
         load_v(j);
       }
@@ -260,8 +260,8 @@ __global__ void __launch_bounds__(THREADS, 2) attn_prefill_tc_kernel(
         umma_commit(&s_full[j & 1]);
         umma_commit(&k_free[j % STAGES]);
       };
-      bool ok = mbar_wait(q_full, 0, err, failed);
-      if (ok) ok = mbar_wait(&k_full[0], 0, err, failed);
+      bool ok = mbar_wait(q_full, 0, err, failed, 4);
+      if (ok) ok = mbar_wait(&k_full[0], 0, err, failed, 5);
       if (ok) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         issue_s(0);
@@ -269,13 +269,13 @@ __global__ void __launch_bounds__(THREADS, 2) attn_prefill_tc_kernel(
       for (int j = 0; j < n_tiles && ok; ++j) {
         if (j + 1 < n_tiles) {
           // S of the next tile goes into the other buffer: the P V product that read it was issued before
-          ok = mbar_wait(&k_full[(j + 1) % STAGES], (unsigned)(((j + 1) / STAGES) & 1), err, failed);
+          ok = mbar_wait(&k_full[(j + 1) % STAGES], (unsigned)(((j + 1) / STAGES) & 1), err, failed, 6);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
           issue_s(j + 1);
         }
-        ok = mbar_wait(&v_full[j % STAGES], (unsigned)((j / STAGES) & 1), err, failed);
-        if (ok) ok = mbar_wait(&p_ready[j & 1], (unsigned)((j >> 1) & 1), err, failed);
+        ok = mbar_wait(&v_full[j % STAGES], (unsigned)((j / STAGES) & 1), err, failed, 7);
+        if (ok) ok = mbar_wait(&p_ready[j & 1], (unsigned)((j >> 1) & 1), err, failed, 8);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const unsigned char* vs = v_s + (size_t)(j % STAGES) * V_BYTES;
@@ -298,7 +298,7 @@ __global__ void __launch_bounds__(THREADS, 2) attn_prefill_tc_kernel(
     float m_run = -INFINITY, l_run = 0.f;
     bool ok = true;
     for (int j = 0; j < n_tiles; ++j) {
-      ok = mbar_wait(&s_full[j & 1], (unsigned)((j >> 1) & 1), err, failed);
+      ok = mbar_wait(&s_full[j & 1], (unsigned)((j >> 1) & 1), err, failed, 9);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -338,7 +338,7 @@ __global__ void __launch_bounds__(THREADS, 2) attn_prefill_tc_kernel(
         if (j > 0) {
           // S of tile j is done, hence every product issued before it, the P V of tile j-2 among them: the
           // barrier is in phase j-1 or j, which one parity bit tells apart
-          ok = mbar_wait(o_done, (unsigned)((j - 1) & 1), err, failed);   // O holds tiles 0 .. j-1
+          ok = mbar_wait(o_done, (unsigned)((j - 1) & 1), err, failed, 10);   // O holds tiles 0 .. j-1
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -366,18 +366,21 @@ __global__ void __launch_bounds__(THREADS, 2) attn_prefill_tc_kernel(
       tmem_st32(s_addr, pk);   // P over the first half of its own S buffer
       tmem_st_wait();
       l_run = l_run * alpha + sum;
+      if (j > 0 && j == n_tiles - 1) {
+        // A parity wait tells two phases apart, not three.  Having seen S of the last tile only proves the
+        // P V product of tile n-3 done.  The one of tile n-2 is awaited here, while the last one cannot have
+        // run (it needs this thread's arrival below): the barrier is in phase n-2 or n-1.  After the arrival
+        // it is in phase n-1 or n, which the wait behind the loop tells apart.  (Waiting for both behind the
+        // loop would hang a thread that slept through phase n-1.)
+        ok = mbar_wait(o_done, (unsigned)((j - 1) & 1), err, failed, 20);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+      }
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       mbar_arrive(&p_ready[j & 1]);
     }
-    if (ok && n_tiles >= 2) {
-      // A parity wait tells two phases apart, not three.  This thread last saw S of the last tile, which
-      // only proves the P V product of tile n-3 done; the one of tile n-2 was issued after that S.  So
-      // first the phase of tile n-2 (else, were it still running, its parity would pass for "n-1 done")
-      ok = mbar_wait(o_done, (unsigned)((n_tiles - 2) & 1), err, failed);
-      ok = __all_sync(0xffffffffu, ok);
-    }
     if (ok) {
-      ok = mbar_wait(o_done, (unsigned)((n_tiles - 1) & 1), err, failed);
+      ok = mbar_wait(o_done, (unsigned)((n_tiles - 1) & 1), err, failed, 12);
       ok = __all_sync(0xffffffffu, ok);
     }
     if (ok) {

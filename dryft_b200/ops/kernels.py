@@ -288,10 +288,11 @@ def error_flag(device: torch.device) -> torch.Tensor:
 def check_error_flags() -> None:
     """Raise if any kernel gave up a bounded wait since the last check (reads the flag: a sync)."""
     for idx, flag in _error_flags.items():
-        if int(flag.item()) != 0:
+        code = int(flag.item())
+        if code != 0:
             flag.zero_()
-            raise KernelError(f"a kernel on cuda:{idx} gave up waiting for its own copies (bounded wait ran out); "
-                              "results since the last check are not valid")
+            raise KernelError(f"a kernel on cuda:{idx} gave up waiting for its own copies (bounded wait ran out, "
+                              f"place {code}); results since the last check are not valid")
 
 
 def _ok(rc: int, what: str, n_kernels: int = 1) -> None:
