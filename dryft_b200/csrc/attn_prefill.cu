@@ -88,7 +88,10 @@ __global__ void __launch_bounds__(THREADS) attn_prefill_kernel(
   bf16* ks = qs + BM * KS;                        // [2][BN][KS]
   bf16* vs = ks + 2 * BN * KS;                    // [2][BN][KS]
 
-  const int tile = blockIdx.x, h = blockIdx.y, kvh = h / G;
+  // Heads run fastest: the host lists the tiles with the most keys first, so all heads of the longest
+  // tiles start first and the short ones fill the gaps at the end (with tiles fastest, every head's
+  // longest tile would be spread over the launch and the last of them would finish alone).
+  const int tile = blockIdx.x / nH, h = blockIdx.x % nH, kvh = h / G;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int tok0 = tile_tok0[tile], rows = tile_rows[tile];
@@ -259,7 +262,8 @@ DRYFT_API int dryft_attn_prefill(const void* q, const void* k_pages, const void*
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  dim3 grid(n_tiles, nH);
+  if ((long long)n_tiles * nH > 2147483647LL) return DRYFT_ERR_UNSUPPORTED;
+  dim3 grid((unsigned)(n_tiles * nH));
   attn_prefill_kernel<<<grid, THREADS, smem, st>>>((const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, page_table,
                                                   max_pages, tile_tok0, tile_rows, tok_slot, tok_pos, (bf16*)out, nH, nKV,
                                                   scale * 1.4426950408889634f, window);

@@ -178,7 +178,10 @@ __global__ void __launch_bounds__(THREADS, 2) attn_prefill_tc_kernel(
   __shared__ int failed_s;
   volatile int* failed = &failed_s;
 
-  const int tile = blockIdx.x, h = blockIdx.y, kvh = h / G;
+  // Heads run fastest: the host lists the tiles with the most keys first, so all heads of the longest
+  // tiles start first and the short ones fill the gaps at the end (with tiles fastest, every head's
+  // longest tile would be spread over the launch and the last of them would finish alone).
+  const int tile = blockIdx.x / nH, h = blockIdx.x % nH, kvh = h / G;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tok0 = tile_tok0[tile], rows = tile_rows[tile];
   const int slot = tok_slot[tok0];
@@ -479,7 +482,8 @@ DRYFT_API int dryft_attn_prefill_tc(const void* q, const void* k_pages, const vo
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  dim3 grid(n_tiles, nH);
+  if ((long long)n_tiles * nH > 2147483647LL) return DRYFT_ERR_UNSUPPORTED;
+  dim3 grid((unsigned)(n_tiles * nH));
   attn_prefill_tc_kernel<<<grid, THREADS, SMEM_BYTES, st>>>(map_q, map_k, map_v, page_table, max_pages, tile_tok0, tile_rows,
                                                            tok_slot, tok_pos, (bf16*)out, nH, nKV,
                                                            scale * 1.4426950408889634f, window, err);
