@@ -375,6 +375,141 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) qk_norm_rope_store_fast_kerne
   }
 }
 
+// bfloat16 with a cos / sin table, head sizes 16 * LPH (LPH = 1, 2, 4, 8 or 16 lanes a head): 16-byte loads
+// and stores throughout.  A lane holds 8 elements of the first half of a head and the 8 they pair with in
+// the second half; 32 / LPH heads go side by side in a warp, ROPE_VEC_PASSES such groups per warp, all
+// loads issued before the first use.  Same formulas and roundings as the kernel above.
+constexpr int ROPE_VEC_PASSES = 3;
+__device__ __forceinline__ __nv_bfloat162 pair_of(const uint4& v, int e) {   // e is a constant after unrolling
+  const unsigned u = e == 0 ? v.x : e == 1 ? v.y : e == 2 ? v.z : v.w;
+  return *reinterpret_cast<const __nv_bfloat162*>(&u);
+}
+__device__ __forceinline__ unsigned bits_of(__nv_bfloat162 v) { return *reinterpret_cast<unsigned*>(&v); }
+template <int LPH>
+__global__ void __launch_bounds__(ROPE_WARPS * 32) qk_norm_rope_store_vec_kernel(
+    const __nv_bfloat16* __restrict__ qkv, int qkv_stride, const float* __restrict__ wq, const float* __restrict__ wk,
+    const __nv_bfloat16* __restrict__ cs_table, const int* __restrict__ tok_slot, const int* __restrict__ tok_pos,
+    __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages,
+    const int* __restrict__ page_table, int max_pages, int nH, int nKV, int page_size, float eps, int has_norm, int write_kv) {
+  typedef __nv_bfloat16 bf16;
+  typedef __nv_bfloat162 bf162;
+  constexpr int D = 16 * LPH, half = D / 2, HPP = 32 / LPH;
+  const int lane = threadIdx.x & 31;
+  const int g = lane / LPH, c = lane % LPH;
+  const int heads_total = nH + (write_kv ? 2 * nKV : 0);
+  const int n = blockIdx.x;
+  const int head0 = (blockIdx.y * ROPE_WARPS + (threadIdx.x >> 5)) * (HPP * ROPE_VEC_PASSES);
+  if (head0 >= heads_total) return;
+  const bf16* row = qkv + (size_t)n * qkv_stride;
+  uint4 a[ROPE_VEC_PASSES], b[ROPE_VEC_PASSES];
+#pragma unroll
+  for (int u = 0; u < ROPE_VEC_PASSES; ++u) {
+    const int head = min(head0 + u * HPP + g, heads_total - 1);   // lanes past the last head repeat it and store nothing
+    a[u] = *reinterpret_cast<const uint4*>(row + (size_t)head * D + 8 * c);
+    b[u] = *reinterpret_cast<const uint4*>(row + (size_t)head * D + half + 8 * c);
+  }
+  const int slot = tok_slot[n];
+  const int pos = tok_pos[n];
+  const uint4 cs4 = *reinterpret_cast<const uint4*>(cs_table + (size_t)n * D + 8 * c);
+  const uint4 sn4 = *reinterpret_cast<const uint4*>(cs_table + (size_t)n * D + half + 8 * c);
+  unsigned wqa[4] = {0, 0, 0, 0}, wqb[4] = {0, 0, 0, 0}, wka[4] = {0, 0, 0, 0}, wkb[4] = {0, 0, 0, 0};   // bfloat16 pairs
+  if (has_norm) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 qa = *reinterpret_cast<const float2*>(wq + 8 * c + 2 * e), qb = *reinterpret_cast<const float2*>(wq + half + 8 * c + 2 * e);
+      const float2 ka = *reinterpret_cast<const float2*>(wk + 8 * c + 2 * e), kb = *reinterpret_cast<const float2*>(wk + half + 8 * c + 2 * e);
+      wqa[e] = bits_of(__floats2bfloat162_rn(qa.x, qa.y)); wqb[e] = bits_of(__floats2bfloat162_rn(qb.x, qb.y));
+      wka[e] = bits_of(__floats2bfloat162_rn(ka.x, ka.y)); wkb[e] = bits_of(__floats2bfloat162_rn(kb.x, kb.y));
+    }
+  }
+  if (slot < 0) {
+    // padding token: a defined (zero) query, nothing cached
+#pragma unroll
+    for (int u = 0; u < ROPE_VEC_PASSES; ++u) {
+      const int head = head0 + u * HPP + g;
+      if (head < nH) {
+        *reinterpret_cast<uint4*>(q_out + ((size_t)n * nH + head) * D + 8 * c) = make_uint4(0, 0, 0, 0);
+        *reinterpret_cast<uint4*>(q_out + ((size_t)n * nH + head) * D + half + 8 * c) = make_uint4(0, 0, 0, 0);
+      }
+    }
+    return;
+  }
+  size_t page_off = 0;
+  if (write_kv)
+    page_off = ((size_t)page_table[(size_t)slot * max_pages + pos / page_size] * nKV * page_size + (pos % page_size)) * D;
+  float inv[ROPE_VEC_PASSES];
+#pragma unroll
+  for (int u = 0; u < ROPE_VEC_PASSES; ++u) {
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 x = __bfloat1622float2(pair_of(a[u], e)), y = __bfloat1622float2(pair_of(b[u], e));
+      ss += x.x * x.x + x.y * x.y + y.x * y.x + y.y * y.y;
+    }
+    inv[u] = ss;
+  }
+  if (has_norm) {
+#pragma unroll
+    for (int o = LPH / 2; o > 0; o >>= 1)
+#pragma unroll
+      for (int u = 0; u < ROPE_VEC_PASSES; ++u) inv[u] += __shfl_xor_sync(0xffffffffu, inv[u], o);
+#pragma unroll
+    for (int u = 0; u < ROPE_VEC_PASSES; ++u) inv[u] = rsqrtf(inv[u] / (float)D + eps);
+  }
+#pragma unroll
+  for (int u = 0; u < ROPE_VEC_PASSES; ++u) {
+    const int head = head0 + u * HPP + g;
+    if (head >= heads_total) continue;
+    bf16* dst;
+    const bool is_q = head < nH;
+    if (is_q) {
+      dst = q_out + ((size_t)n * nH + head) * D;
+    } else {
+      const int kvh = (head - nH) % nKV;
+      const size_t off = page_off + (size_t)kvh * page_size * D;
+      if (head >= nH + nKV) {  // value head: plain copy
+        *reinterpret_cast<uint4*>(v_pages + off + 8 * c) = a[u];
+        *reinterpret_cast<uint4*>(v_pages + off + half + 8 * c) = b[u];
+        continue;
+      }
+      dst = k_pages + off;
+    }
+    unsigned o1[4], o2[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      // x * inv in 32-bit rounded to a bfloat16 pair; every bfloat16 product and sum below is the exact
+      // result rounded once (the _rn forms are never fused)
+      bf162 x2 = pair_of(a[u], e), y2 = pair_of(b[u], e);
+      const bf162 cs2 = pair_of(cs4, e), sn2 = pair_of(sn4, e);
+      if (has_norm) {
+        const float2 xf = __bfloat1622float2(x2), yf = __bfloat1622float2(y2);
+        const unsigned wa = is_q ? wqa[e] : wka[e], wb = is_q ? wqb[e] : wkb[e];
+        x2 = __hmul2_rn(__floats2bfloat162_rn(xf.x * inv[u], xf.y * inv[u]), *reinterpret_cast<const bf162*>(&wa));
+        y2 = __hmul2_rn(__floats2bfloat162_rn(yf.x * inv[u], yf.y * inv[u]), *reinterpret_cast<const bf162*>(&wb));
+      }
+      o1[e] = bits_of(__hsub2_rn(__hmul2_rn(x2, cs2), __hmul2_rn(y2, sn2)));
+      o2[e] = bits_of(__hadd2_rn(__hmul2_rn(y2, cs2), __hmul2_rn(x2, sn2)));
+    }
+    *reinterpret_cast<uint4*>(dst + 8 * c) = make_uint4(o1[0], o1[1], o1[2], o1[3]);
+    *reinterpret_cast<uint4*>(dst + half + 8 * c) = make_uint4(o2[0], o2[1], o2[2], o2[3]);
+  }
+}
+
+template <int LPH>
+static int launch_vec(const void* qkv, int qkv_stride, const float* wq, const float* wk, const void* cs_table, const int* tok_slot,
+                      const int* tok_pos, void* q_out, void* k_pages, void* v_pages, const int* page_table, int max_pages,
+                      int n_tokens, int nH, int nKV, int page_size, float eps, int has_norm, int write_kv, cudaStream_t st) {
+  typedef __nv_bfloat16 bf16;
+  const int heads_total = nH + (write_kv ? 2 * nKV : 0);
+  const int per_block = ROPE_WARPS * (32 / LPH) * ROPE_VEC_PASSES;
+  const dim3 grid((unsigned)n_tokens, (unsigned)((heads_total + per_block - 1) / per_block));
+  if (grid.y > 65535) return DRYFT_ERR_UNSUPPORTED;
+  qk_norm_rope_store_vec_kernel<LPH><<<grid, ROPE_WARPS * 32, 0, st>>>(
+      (const bf16*)qkv, qkv_stride, wq, wk, (const bf16*)cs_table, tok_slot, tok_pos, (bf16*)q_out, (bf16*)k_pages, (bf16*)v_pages,
+      page_table, max_pages, nH, nKV, page_size, eps, has_norm, write_kv);
+  return launch_status();
+}
+
 // cos / sin of every token's angles, rounded to T: table [n_tokens][2][half]
 template <typename T>
 __global__ void rope_table_kernel(const int* __restrict__ tok_pos, const float* __restrict__ inv_freq, T* __restrict__ table,
@@ -408,6 +543,15 @@ static int launch(const void* qkv, int qkv_stride, const float* wq, const float*
   if (n_tokens <= 0) return 0;
   if (D <= 0 || (R & 1) || R > D || R < 0) return DRYFT_ERR_UNSUPPORTED;
   const int heads_total = nH + (write_kv ? 2 * nKV : 0);
+  if (std::is_same<T, __nv_bfloat16>::value && cs_table != nullptr && R == D && (D == 16 || D == 32 || D == 64 || D == 128 || D == 256) &&
+      qkv_stride % 8 == 0 &&
+      !(((uintptr_t)qkv | (uintptr_t)cs_table | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) &&
+      !(((uintptr_t)wq | (uintptr_t)wk) & 7)) {
+#define DRYFT_ROPE_VEC(L) launch_vec<L>(qkv, qkv_stride, wq, wk, cs_table, tok_slot, tok_pos, q_out, k_pages, v_pages, page_table, \
+                                        max_pages, n_tokens, nH, nKV, page_size, eps, has_norm, write_kv, st)
+    return D == 16 ? DRYFT_ROPE_VEC(1) : D == 32 ? DRYFT_ROPE_VEC(2) : D == 64 ? DRYFT_ROPE_VEC(4) : D == 128 ? DRYFT_ROPE_VEC(8) : DRYFT_ROPE_VEC(16);
+#undef DRYFT_ROPE_VEC
+  }
   if (R == D && (D & 3) == 0 && D <= 256) {
     const int per_block = ROPE_WARPS * ROPE_HPW;
     const dim3 grid((unsigned)n_tokens, (unsigned)((heads_total + per_block - 1) / per_block));

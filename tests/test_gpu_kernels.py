@@ -333,7 +333,9 @@ def _paged_cache(n_pages, n_kv, page, d, dtype, fill=0.0):
 @pytest.mark.parametrize("with_table", [False, True])
 @pytest.mark.parametrize("n_heads,n_kv,d,rot,theta,eps", [(4, 2, 16, 16, 1e4, 1e-6), (6, 2, 48, 48, 5e5, 1e-5),
                                                             (8, 8, 128, 128, 5e6, 1e-6), (3, 1, 64, 32, 1e4, 1e-6),
-                                                            (2, 1, 24, 18, 1e4, 1e-6), (3, 1, 256, 256, 1e6, 1e-6)])
+                                                            (2, 1, 24, 18, 1e4, 1e-6), (3, 1, 256, 256, 1e6, 1e-6),
+                                                            (6, 3, 32, 32, 1e6, 1e-5), (5, 1, 64, 64, 1e4, 1e-6),
+                                                            (32, 8, 128, 128, 5e6, 1e-6)])
 def test_qk_norm_rope_store(dtype, with_table, n_heads, n_kv, d, rot, theta, eps):
     """With the step's cos / sin table and with angles evaluated in the kernel: same result."""
     k = K()
