@@ -69,6 +69,10 @@ class _KVGroup:
         self.page_table_host = torch.zeros((max_slots, max_pages_per_slot), dtype=torch.int32)
         self.page_table = torch.zeros((max_slots, max_pages_per_slot), dtype=torch.int32, device=device)
         self.dirty: set = set()
+        # pinned copy of the rows on their way to the device (one asynchronous copy per flush), and the
+        # event after which it may be rewritten
+        self.staging: Optional[torch.Tensor] = None
+        self.staged: Optional[torch.cuda.Event] = None
 
     def bytes(self) -> int:
         return 2 * self.k.numel() * self.k.element_size()
@@ -220,11 +224,25 @@ class SequenceCache:
                 g.dirty.add(slot)
 
     def flush(self) -> None:
-        """Copy page-table rows that changed to the device (stream-ordered, before the step)."""
+        """Copy page-table rows that changed to the device (stream-ordered, before the step): the span
+        of rows from the first to the last changed one, through a pinned snapshot, as one asynchronous
+        copy per group.  Rows in between that did not change are rewritten with the values they have."""
         for g in self._groups:
-            for s in sorted(g.dirty):
-                g.page_table[s].copy_(g.page_table_host[s], non_blocking=False)
+            if not g.dirty:
+                continue
+            lo, hi = min(g.dirty), max(g.dirty) + 1
             g.dirty.clear()
+            if self.device.type != "cuda":
+                g.page_table[lo:hi].copy_(g.page_table_host[lo:hi])
+                continue
+            if g.staging is None:
+                g.staging = torch.empty_like(g.page_table_host).pin_memory()
+            if g.staged is not None:
+                g.staged.synchronize()   # the copy before this one has read the snapshot
+            g.staging[lo:hi].copy_(g.page_table_host[lo:hi])
+            g.page_table[lo:hi].copy_(g.staging[lo:hi], non_blocking=True)
+            g.staged = torch.cuda.Event()
+            g.staged.record()
 
     def advanced(self, slot: int, n: int) -> None:
         """Record on the host that ``slot`` grew by ``n`` tokens (the device copy is advanced by

@@ -18,6 +18,7 @@ from __future__ import annotations
 
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from ..cache.store import SequenceCache
@@ -55,14 +56,17 @@ class Stepper:
             raise ValueError("step: every sequence of a step brings at least one token")
         if len(set(slots)) != B:
             raise ValueError("step: a slot occurs twice in one step")
+        # the step's integers as arrays: a prompt of thousands of tokens is checked and packed at once
+        parts = [np.asarray(t.cpu() if isinstance(t, torch.Tensor) else t) for t in tokens]
+        if any(a.dtype.kind not in "iu" for a in parts):
+            parts = [np.asarray([int(v) for v in t], dtype=np.int64) for t in tokens]
+        flat = np.concatenate(parts).astype(np.int64, copy=False)
+        if flat.size and (int(flat.min()) < 0 or int(flat.max()) >= vocab):
+            bad = int(flat[(flat < 0) | (flat >= vocab)][0])
+            raise ValueError(f"step: token id {bad} is outside the vocabulary [0, {vocab})")
         cu = [0]
-        flat: List[int] = []
-        for t in tokens:
-            for v in t:
-                if not 0 <= int(v) < vocab:
-                    raise ValueError(f"step: token id {v} is outside the vocabulary [0, {vocab})")
-            flat.extend(int(v) for v in t)
-            cu.append(len(flat))
+        for q in q_lens:
+            cu.append(cu[-1] + q)
         rows: List[int] = []
         for b, w in enumerate(want):
             for i in w:
@@ -76,7 +80,7 @@ class Stepper:
             self.cache.reserve(s, q)
         self.cache.flush()
 
-        N = len(flat)
+        N = int(flat.size)
         tiles0: List[int] = []
         tilesn: List[int] = []
         if not decode:
@@ -89,7 +93,7 @@ class Stepper:
             tilesn = [t[2] for t in order]
         T = len(tiles0)
         W = len(rows)
-        packed = flat + cu + list(slots) + rows + tiles0 + tilesn
+        packed = np.concatenate((flat, np.asarray(cu + list(slots) + rows + tiles0 + tilesn, dtype=np.int64))).astype(np.int32)
         dev = self._upload(packed)
         o = 0
         d_tokens = dev[o:o + N]; o += N
@@ -110,16 +114,16 @@ class Stepper:
             self.cache.advanced(s, q)
         return logits
 
-    def _upload(self, ints: List[int]) -> torch.Tensor:
-        """One host->device copy of the step's integers through pinned memory."""
-        n = len(ints)
+    def _upload(self, ints: np.ndarray) -> torch.Tensor:
+        """One host->device copy of the step's integers (an int32 array) through pinned memory."""
+        n = int(ints.size)
         if self._pinned is None or self._pinned.numel() < n:
             self._pinned = torch.empty(max(n, 4096), dtype=torch.int32, pin_memory=True)
         # the previous step's copy out of this buffer must have finished before it is rewritten
         if self._upload_event is not None:
             self._upload_event.synchronize()
         buf = self._pinned[:n]
-        buf.copy_(torch.tensor(ints, dtype=torch.int32))
+        buf.numpy()[:] = ints
         dev = torch.empty(n, dtype=torch.int32, device=self.rt.device)
         dev.copy_(buf, non_blocking=True)
         self._upload_event = torch.cuda.Event()
