@@ -190,6 +190,8 @@ def main() -> int:
     ap.add_argument("--phase", default="all", choices=["all", "decode", "prefill", "timeline"],
                     help="time only one phase (for profiling); the JSON line then carries only that phase")
     ap.add_argument("--seed", type=int, default=0)
+    ap.add_argument("--small-m-max", type=int, default=None,
+                    help="rows up to which decode products stream weights themselves (the engine's default if not given)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -216,7 +218,8 @@ def main() -> int:
     ctx_cap = args.prompt_len + args.steps + warmup + 64
     eng = Engine.from_config(cfg, seed=args.seed, dtype="bfloat16", max_batch=max_batch,
                              max_seq_len=max(raw["max_position_embeddings"], 2048 + 64),
-                             max_tokens=max(max_batch * (ctx_cap + 64), 4096))
+                             max_tokens=max(max_batch * (ctx_cap + 64), 4096),
+                             **({"small_m_max": args.small_m_max} if args.small_m_max is not None else {}))
     torch.cuda.synchronize()
 
     if args.phase == "prefill":
