@@ -214,10 +214,11 @@ def main() -> int:
         raw["num_hidden_layers"] = args.layers
     cfg = config_from_dict(raw)
     hbm_gbs, bf16_tflops, peak_src = peaks()
-    max_batch = max(64, args.batch)
+    # the full run also measures batch 64; a single phase holds only what its batch needs (long contexts fit)
+    max_batch = max(64, args.batch) if args.phase == "all" else args.batch
     ctx_cap = args.prompt_len + args.steps + warmup + 64
     eng = Engine.from_config(cfg, seed=args.seed, dtype="bfloat16", max_batch=max_batch,
-                             max_seq_len=max(raw["max_position_embeddings"], 2048 + 64),
+                             max_seq_len=max(raw["max_position_embeddings"], 2048 + 64, ctx_cap),
                              max_tokens=max(max_batch * (ctx_cap + 64), 4096),
                              **({"small_m_max": args.small_m_max} if args.small_m_max is not None else {}))
     torch.cuda.synchronize()
