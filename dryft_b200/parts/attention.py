@@ -111,6 +111,11 @@ class Attention:
         pages = (max(1, max_kv) + self.rt.page_size - 1) // self.rt.page_size
         room = max(1, self.rt.sm_count // max(1, n_rows * self.n_kv))
         by_cluster = min((pages + 2) // 3, room, self.CLUSTER_SPLITS)
+        if by_cluster > 4 and n_rows * self.n_kv > 8:
+            # a cluster of 5..8 blocks (one block a SM) needs that many free SMs in one GPC: with more than
+            # eight such clusters some wait for a whole GPC's worth of SMs (batch 2 at 2,063 keys: 20.8 us a
+            # layer with 16 clusters of 8 against 12.9 us with 16 clusters of 4)
+            by_cluster = 4
         if pages <= 16 and 4 * n_rows * self.n_kv > self.rt.sm_count:
             by_cluster = 1   # up to 1,024 keys a block's eight warps are enough unless most SMs would idle
         by_memory = min(32, (max(1, max_kv) + 1023) // 1024)

@@ -30,4 +30,6 @@ def test_decode_splits_of_a_long_single_sequence():
     assert _splits(16384, 1) == 16
     assert _splits(8192, 1) == 8        # up to eight splits are one cluster
     assert _splits(8192, 8) == 2        # batch 8: 64 pairs, two splits each
+    assert _splits(4096, 2) == 4        # 16 clusters: of four blocks, not of eight
+    assert _splits(4096, 1) == 8
     assert _splits(512, 64) == 1
