@@ -240,7 +240,14 @@ def attention_prefill_lib(head_dim: int, group: int, page: int) -> ctypes.CDLL:
 
 
 # ----------------------------------------------------------------------------- argument checks
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> ctypes.c_void_p:
+    """The current stream's handle (also inside a graph capture).  A prompt step makes hundreds of launches;
+    the raw accessor costs a fraction of a microsecond, the Stream object about fifteen."""
+    if _raw_stream is not None:
+        return ctypes.c_void_p(_raw_stream(torch.cuda.current_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
