@@ -87,11 +87,11 @@ def test_page_ledger_growth_close_and_window():
     assert w.pool.n_free == 4
 
 
-def _cache(window=None, max_tokens=512, slots=3, state=False):
+def _cache(window=None, max_tokens=512, slots=3, state=False, device="cpu"):
     needs = [(KVNeed(2, 16, None), None), (KVNeed(2, 16, window), StateNeed((4,), torch.float32) if state else None),
              (KVNeed(2, 16, None), None)]
     return SequenceCache(needs, [None, None, 0], max_tokens=max_tokens, max_slots=slots, max_seq_len=256, page_size=64,
-                         dtype=torch.float32, device=torch.device("cpu"))
+                         dtype=torch.float32, device=torch.device(device))
 
 
 def test_groups_have_storage_of_their_own_and_borrowers_share():
@@ -170,9 +170,9 @@ def test_state_is_zeroed_when_a_slot_is_reused():
     assert s2 == s and float(st[s].abs().max()) == 0.0 and int(c.seq_len[s]) == 0 and int(c.last_token[s]) == 0
 
 
-def test_random_traffic_never_loses_a_page():
+def _random_traffic(device):
     rng = random.Random(1)
-    c = _cache(window=40, max_tokens=1024, slots=3)
+    c = _cache(window=40, max_tokens=1024, slots=3, device=device)
     live = {}
     for _ in range(400):
         r = rng.random()
@@ -191,6 +191,8 @@ def test_random_traffic_never_loses_a_page():
             except CacheError:
                 continue
             c.flush()
+            for g in c._groups:   # after a flush the device's page tables are the host's, row for row
+                assert torch.equal(g.page_table.cpu(), g.page_table_host)
             c.advanced(s, n)
             live[s] += n
             assert c.len_host[s] == live[s]
@@ -198,3 +200,13 @@ def test_random_traffic_never_loses_a_page():
     c.close_sequences(sorted(live))
     c.check()
     assert c.free_tokens() == 1024
+
+
+def test_random_traffic_never_loses_a_page():
+    _random_traffic("cpu")
+
+
+@pytest.mark.gpu
+def test_random_traffic_on_the_device_keeps_the_page_tables_equal():
+    """The same traffic with the tables on the GPU: changed rows travel as one pinned asynchronous copy."""
+    _random_traffic("cuda:0")
