@@ -256,6 +256,13 @@ def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
 
 
 def _need(t: torch.Tensor, name: str, dtype=None, shape=None) -> torch.Tensor:
+    # the common case first (a prompt step makes a thousand of these checks); what fails it is named below
+    try:
+        if t.is_cuda and t.is_contiguous() and (dtype is None or t.dtype == dtype) and (
+                shape is None or (len(shape) == t.dim() and all(s is None or s == d for s, d in zip(shape, t.shape)))):
+            return t
+    except AttributeError:
+        pass
     if not isinstance(t, torch.Tensor):
         raise KernelError(f"{name}: expected a tensor, got {type(t).__name__}")
     if t.device.type != "cuda":
