@@ -20,8 +20,14 @@ head) with random weights, a batch of 8 sequences with 512-token prompts, and ti
 
 The method follows hari495/dryft's ``agent/bench.py:96-126`` (warm-up, synchronize on both sides,
 seeded uniform token ids, ``bench.py:111-119``); its achieved-bandwidth figure (``bench.py:171-172``) is
-the ``roofline`` entry.  The reference arm is unavailable: hari495/dryft has neither setup.py nor
-pyproject.toml, so ``pip install --no-index ... <its checkout>`` refuses it.
+the ``roofline`` entry.
+
+``--impl reference`` times hari495/dryft itself for the same metric: its unmodified ``engine/`` folder
+(kept under ``baseline/_ref/engine``; the project has no setup.py or pyproject.toml, so it is a plain copy
+rather than a pip install) is put on ``sys.path`` and driven through its own public entry point,
+``Engine(model_path).generate(input_ids, max_new_tokens)`` (``engine/engine.py:28-30,138-166``), on a
+Qwen3-4B-shaped random-weights folder written to a temporary directory.  Nothing of ``dryft_b200`` is
+imported on that path.
 """
 
 import argparse
@@ -176,6 +182,145 @@ def prefill_time(eng, tokens, iters, seed):
     return statistics.median(times)
 
 
+# ----------------------------------------------------------------------------- the reference arm
+REF_ENGINE_DIR = os.path.join(ROOT, "baseline", "_ref", "engine")
+
+# the checkpoint facts hari495/dryft pins (engine/dryft_qwen3/config.py:53-70): the benchmark shape
+REF_CONFIG = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hidden_layers": 36, "hidden_size": 2560,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 9728,
+    "hidden_act": "silu", "vocab_size": 151936, "tie_word_embeddings": True, "rms_norm_eps": 1e-6,
+    "rope_theta": 5000000, "rope_scaling": None, "max_position_embeddings": 262144, "attention_bias": False,
+    "torch_dtype": "bfloat16",
+}
+
+
+def write_reference_model(out_dir, seed):
+    """config.json + model.safetensors of the benchmark shape: normal(0, 0.02) matrices, norm weights
+    1 + normal(0, 0.02), bfloat16, tied head (no lm_head.weight).  Drawn on the GPU (4 G values), saved once."""
+    import torch
+    from safetensors.torch import save_file
+
+    c = REF_CONFIG
+    H, D, I, V = c["hidden_size"], c["head_dim"], c["intermediate_size"], c["vocab_size"]
+    Hq, Hkv = c["num_attention_heads"] * D, c["num_key_value_heads"] * D
+    gen = torch.Generator(device="cuda").manual_seed(seed)
+
+    def mat(*shape):
+        return (torch.randn(shape, generator=gen, device="cuda", dtype=torch.float32) * 0.02).to(torch.bfloat16).cpu()
+
+    def vec(n):
+        return (1.0 + torch.randn((n,), generator=gen, device="cuda", dtype=torch.float32) * 0.02).to(torch.bfloat16).cpu()
+
+    t = {"model.embed_tokens.weight": mat(V, H), "model.norm.weight": vec(H)}
+    for i in range(c["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        t[p + "input_layernorm.weight"] = vec(H)
+        t[p + "self_attn.q_proj.weight"] = mat(Hq, H)
+        t[p + "self_attn.k_proj.weight"] = mat(Hkv, H)
+        t[p + "self_attn.v_proj.weight"] = mat(Hkv, H)
+        t[p + "self_attn.q_norm.weight"] = vec(D)
+        t[p + "self_attn.k_norm.weight"] = vec(D)
+        t[p + "self_attn.o_proj.weight"] = mat(H, Hq)
+        t[p + "post_attention_layernorm.weight"] = vec(H)
+        t[p + "mlp.gate_proj.weight"] = mat(I, H)
+        t[p + "mlp.up_proj.weight"] = mat(I, H)
+        t[p + "mlp.down_proj.weight"] = mat(H, I)
+    os.makedirs(out_dir, exist_ok=True)
+    with open(os.path.join(out_dir, "config.json"), "w", encoding="utf-8") as f:
+        json.dump(c, f, indent=1)
+    save_file(t, os.path.join(out_dir, "model.safetensors"), metadata={"format": "pt"})
+
+
+def reference_arm(args) -> int:
+    """hari495/dryft's own engine on the same metric and shape (batch 8, 512-token prompts, K decode steps).
+    ``value`` = batch x K / the time between the first and the last yield of ``generate(ids, K + 1)``:
+    host token lists in, a host list out per step, so it is an end-to-end number and ``e2e`` repeats it."""
+    import shutil
+    import tempfile
+
+    def unavailable(why):
+        print(json.dumps({"impl": "reference", "unavailable": why}))
+        return 0
+
+    if not os.path.isfile(os.path.join(REF_ENGINE_DIR, "engine.py")):
+        return unavailable("baseline/_ref/engine/engine.py is absent (hari495/dryft has no setup.py or pyproject.toml to "
+                           "pip-install; its engine/ folder is copied there by hand)")
+    if args.gpus != 1:
+        return unavailable("hari495/dryft is a single-GPU engine (no torch.distributed call site)")
+    try:
+        import torch
+        if not torch.cuda.is_available():
+            return unavailable("no CUDA device")
+        import triton  # noqa: F401  (the reference imports it directly)
+    except Exception as e:  # noqa: BLE001
+        return unavailable(f"import failed: {e!r}")
+    warmup = max(3, args.warmup)
+    batch, prompt_len, steps = args.batch, args.prompt_len, args.steps
+    tmp = tempfile.mkdtemp(prefix="dryft-ref-model-")
+    try:
+        t0 = time.time()
+        write_reference_model(tmp, args.seed)
+        print(f"[bench] reference: wrote the random-weights folder in {time.time() - t0:.0f}s", file=sys.stderr, flush=True)
+        sys.path.insert(0, REF_ENGINE_DIR)
+        try:
+            from engine import Engine as RefEngine  # baseline/_ref/engine/engine.py
+            eng = RefEngine(tmp)
+        except Exception as e:  # noqa: BLE001
+            return unavailable(f"hari495/dryft's Engine(model_path) failed here: {e!r}"[:400])
+        kernels = {n: getattr(eng.model, a, None) is not None for n, a in
+                   (("rmsnorm", "_k_rms"), ("rope_qknorm", "_k_rope"), ("attn_decode", "_k_attn"), ("silu_mul", "_k_silu"))}
+        prompts = random_prompts(batch, prompt_len, REF_CONFIG["vocab_size"], args.seed)
+        for _ in eng.generate(prompts, warmup + 1):
+            pass
+        torch.cuda.synchronize()
+        clocks = ClockSampler()
+        clocks.start()
+        t_first, n = None, 0
+        for out in eng.generate(prompts, steps + 1):
+            if t_first is None:
+                torch.cuda.synchronize()
+                t_first = time.perf_counter()
+            n += 1
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t_first
+        clock_info = clocks.stop()
+        assert n == steps + 1 and len(out) == batch
+        value = batch * steps / dt
+        T = 2048
+        long_prompt = random_prompts(1, T, REF_CONFIG["vocab_size"], args.seed + 2)
+        pf = []
+        for i in range(5):
+            torch.cuda.synchronize()
+            t1 = time.perf_counter()
+            for _ in eng.generate(long_prompt, 1):
+                pass
+            torch.cuda.synchronize()
+            if i >= 2:
+                pf.append((time.perf_counter() - t1) * 1e3)
+        pf_ms = statistics.median(pf)
+        line = {
+            "metric": "decode tok/s @ batch 8; Qwen3-4B shape BF16 (points: batch 1/64; prefill tok/s @ 2048 tok)",
+            "value": value, "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": dt / steps * 1e3,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic: seeded uniform token ids, random normal(0,0.02) weights", "impl": "reference",
+            "config": {"model": "qwen3-4b", "layers": 36, "layers_of_shape": 36, "hidden": 2560, "q_heads": 32, "kv_heads": 8,
+                       "head_dim": 128, "intermediate": 9728, "vocab": 151936, "tied_head": True, "global_batch": batch,
+                       "seq_len": prompt_len, "parallelism": "single-gpu", "cuda_graphs": eng.graphs is not None,
+                       "timing": "host clock between the first and last yield of Engine.generate, synchronized",
+                       "triton_kernels_on": ",".join(k for k, v in kernels.items() if v) or "none (torch path)",
+                       "speculation": bool(getattr(eng, "spec_ok", False))},
+            # the reference's loop copies its int64 next tokens to a pinned ring every step; its inputs stay on the device
+            "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 8 * batch},
+            "prefill": {"value": T / (pf_ms * 1e-3), "tokens": T, "ms": pf_ms},
+            "clocks": clock_info,
+        }
+        print(json.dumps(line))
+        return 0
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -195,9 +340,7 @@ def main() -> int:
     args = ap.parse_args()
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable": "hari495/dryft has no setup.py or pyproject.toml; pip install "
-                          "--no-index --target baseline/_ref <reference checkout> fails with 'Directory is not installable'"}))
-        return 0
+        return reference_arm(args)
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not measured")
         return 2

@@ -320,12 +320,19 @@ __global__ void __launch_bounds__(NWARP * 32) attn_decode_kernel(const Params p)
     __syncwarp();
     bf16* kst = stage + (size_t)st * 2 * SLICE * KS;
     bf16* vst = kst + SLICE * KS;
-    if (owns_new && sl == pos / SLICE) {  // the staged copy of the token's own row may predate its write
+    if (sl == pos / SLICE) {
       const int r = pos % SLICE;
-      for (int i = lane; i < CPR; i += 32) {
-        *reinterpret_cast<uint4*>(kst + r * KS + i * 8) = *reinterpret_cast<const uint4*>(new_k + i * 8);
-        *reinterpret_cast<uint4*>(vst + r * KS + i * 8) = *reinterpret_cast<const uint4*>(new_v + i * 8);
+      if (owns_new) {  // the staged copy of the token's own row may predate its write
+        for (int i = lane; i < CPR; i += 32) {
+          *reinterpret_cast<uint4*>(kst + r * KS + i * 8) = *reinterpret_cast<const uint4*>(new_k + i * 8);
+          *reinterpret_cast<uint4*>(vst + r * KS + i * 8) = *reinterpret_cast<const uint4*>(new_v + i * 8);
+        }
       }
+      // The rows behind the token's own hold what the page's last holder left.  Their keys are masked below
+      // (probability exactly zero), but 0 * v is only 0 for a finite v: the staged values are zeroed
+      // (the reference zeroes its whole cache once for the same reason, engine/dryft_qwen3/cache.py:43-47).
+      for (int i = lane; i < (SLICE - 1 - r) * CPR; i += 32)
+        *reinterpret_cast<uint4*>(vst + (r + 1 + i / CPR) * KS + (i % CPR) * 8) = make_uint4(0, 0, 0, 0);
       __syncwarp();
     }
 

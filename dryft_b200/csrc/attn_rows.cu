@@ -226,11 +226,19 @@ int launch(const void* q, const void* k_pages, const void* v_pages, const int* p
   if (n_splits > 1 && (!part_o || !part_ml)) return DRYFT_ERR_UNSUPPORTED;
   const size_t smem = Smem<T>::bytes();
   if (smem > 227 * 1024) return DRYFT_ERR_UNSUPPORTED;
-  static bool attr_set = false;  // per instantiation; set outside any stream capture by the first (eager) launch
-  if (smem > 48 * 1024 && !attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(attn_rows_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  // per instantiation and per device (the attribute belongs to the device's copy of the kernel); set outside any
+  // stream capture by the first (eager) launch on that device
+  static bool attr_set[64] = {false};
+  if (smem > 48 * 1024) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
-    attr_set = true;
+    if (dev < 0 || dev >= 64) return DRYFT_ERR_UNSUPPORTED;
+    if (!attr_set[dev]) {
+      e = cudaFuncSetAttribute(attn_rows_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+      attr_set[dev] = true;
+    }
   }
   dim3 grid(n_rows, nKV, n_splits);
   attn_rows_kernel<T><<<grid, THREADS, smem, st>>>((const T*)q, (const T*)k_pages, (const T*)v_pages, page_table,
@@ -274,12 +282,14 @@ DRYFT_API int dryft_attn_rows_static_scratch(int is_bf16, const void* q, const v
                                              void* out, int n_rows, int nKV, int n_splits, float scale, int window,
                                              cudaStream_t st) {
   if (n_rows <= 0) return 0;
-  if (n_splits < 1 || nKV < 1) return DRYFT_ERR_UNSUPPORTED;
-  // partial outputs [rows, heads, splits, D] and (max, sum) pairs [rows, heads, splits, 2]
-  const unsigned long long heads = (unsigned long long)nKV * G;
+  if (n_splits < 1 || nKV < 1 || nKV > 65535 || n_splits > 65535) return DRYFT_ERR_UNSUPPORTED;  // the grid's limits
+  // partial outputs [rows, heads, splits, D] and (max, sum) pairs [rows, heads, splits, 2].  The size check divides
+  // instead of multiplying, so that no count, however large, can wrap around and pass.
+  const unsigned long long heads = (unsigned long long)nKV * G;                      // < 2^20
+  const unsigned long long per_row = heads * (unsigned long long)n_splits * (D + 2);  // < 2^45
+  if (n_splits > 1 && (unsigned long long)n_rows > (unsigned long long)DRYFT_ATTN_ROWS_STATIC_FLOATS / per_row)
+    return DRYFT_ERR_SCRATCH_TOO_SMALL;
   const unsigned long long need_o = (unsigned long long)n_rows * heads * n_splits * D;
-  const unsigned long long need_ml = (unsigned long long)n_rows * heads * n_splits * 2;
-  if (n_splits > 1 && need_o + need_ml > (unsigned long long)DRYFT_ATTN_ROWS_STATIC_FLOATS) return DRYFT_ERR_SCRATCH_TOO_SMALL;
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;

@@ -39,6 +39,27 @@ template <> __device__ __forceinline__ void store2<__nv_bfloat16>(__nv_bfloat16*
   *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
 }
 
+// The rows of a token's page behind its own row, for one kv head, set to zero: `lanes` lanes (this one is
+// `lane_in`) share the work.  Done by the value head of a sequence's last token of a step when the step's
+// attention reads whole pages (tensor-core tiles): a page keeps what its last holder left there, the masked
+// keys get probability zero, and 0 * v must stay 0 whatever v was (the reference zeroes its whole dense
+// cache once instead, engine/dryft_qwen3/cache.py:43-47).
+template <typename T>
+__device__ __forceinline__ void zero_rows_behind(T* next_row, int n_rows, int D, int lane_in, int lanes) {
+  const long long n = (long long)n_rows * D;
+  if (((uintptr_t)next_row & 15) == 0 && (D * sizeof(T)) % 16 == 0) {
+    uint4* p = reinterpret_cast<uint4*>(next_row);
+    const long long n16 = n * (long long)sizeof(T) / 16;
+    for (long long i = lane_in; i < n16; i += lanes) p[i] = make_uint4(0, 0, 0, 0);
+  } else {
+    for (long long i = lane_in; i < n; i += lanes) next_row[i] = from_f32<T>(0.f);
+  }
+}
+// whether packed token n is the last one its sequence brings in this step (tokens of a sequence are consecutive)
+__device__ __forceinline__ bool last_of_sequence(const int* __restrict__ tok_slot, int n, int n_tokens, int slot) {
+  return n + 1 >= n_tokens || tok_slot[n + 1] != slot;
+}
+
 // A lane holds rotary pairs (j, j + R/2), two neighbouring j at a time; the head is read once,
 // normalised, rotated and written.
 constexpr int ROPE_WARPS = 4;
@@ -54,7 +75,7 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) qk_norm_rope_store_kernel(
     T* __restrict__ q_out,                                      // [N, nH, D]
     T* __restrict__ k_pages, T* __restrict__ v_pages,           // [pages, nKV, page_size, D]
     const int* __restrict__ page_table, int max_pages,
-    int n_tokens, int nH, int nKV, int D, int R, int page_size, float eps, int has_norm, int write_kv) {
+    int n_tokens, int nH, int nKV, int D, int R, int page_size, float eps, int has_norm, int write_kv, int zero_tail) {
   // a warp per (token, head): plenty of warps in flight hide the latency of the few loads each one has;
   // grid (tokens, groups of ROPE_WARPS heads)
   const int lane = threadIdx.x & 31;
@@ -118,6 +139,8 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) qk_norm_rope_store_kernel(
         } else {
           for (int i = lane; i < D; i += 32) vd[i] = src[i];
         }
+        if (zero_tail && last_of_sequence(tok_slot, n, n_tokens, slot))
+          zero_rows_behind<T>(vd + D, page_size - 1 - pos % page_size, D, lane, 32);
         continue;
       }
       dst = k_pages + off;
@@ -217,7 +240,7 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) qk_norm_rope_store_fast_kerne
     const float* __restrict__ inv_freq, const T* __restrict__ cs_table, const int* __restrict__ tok_slot,
     const int* __restrict__ tok_pos, T* __restrict__ q_out, T* __restrict__ k_pages, T* __restrict__ v_pages,
     const int* __restrict__ page_table, int max_pages, int nH, int nKV, int D, int page_size, float eps, int has_norm,
-    int write_kv) {
+    int write_kv, int zero_tail) {
   const int lane = threadIdx.x & 31;
   const int heads_total = nH + (write_kv ? 2 * nKV : 0);
   const int n = blockIdx.x;
@@ -330,6 +353,8 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) qk_norm_rope_store_fast_kerne
             store2<T>(v_pages + off + j + half, b[u][i][0], b[u][i][1]);
           }
         }
+        if (zero_tail && last_of_sequence(tok_slot, n, (int)gridDim.x, slot))
+          zero_rows_behind<T>(v_pages + off + D, page_size - 1 - pos % page_size, D, lane, 32);
         continue;
       }
       dst = k_pages + off;
@@ -390,7 +415,8 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) qk_norm_rope_store_vec_kernel
     const __nv_bfloat16* __restrict__ qkv, int qkv_stride, const float* __restrict__ wq, const float* __restrict__ wk,
     const __nv_bfloat16* __restrict__ cs_table, const int* __restrict__ tok_slot, const int* __restrict__ tok_pos,
     __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ k_pages, __nv_bfloat16* __restrict__ v_pages,
-    const int* __restrict__ page_table, int max_pages, int nH, int nKV, int page_size, float eps, int has_norm, int write_kv) {
+    const int* __restrict__ page_table, int max_pages, int nH, int nKV, int page_size, float eps, int has_norm, int write_kv,
+    int zero_tail) {
   typedef __nv_bfloat16 bf16;
   typedef __nv_bfloat162 bf162;
   constexpr int D = 16 * LPH, half = D / 2, HPP = 32 / LPH;
@@ -470,6 +496,8 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) qk_norm_rope_store_vec_kernel
       if (head >= nH + nKV) {  // value head: plain copy
         *reinterpret_cast<uint4*>(v_pages + off + 8 * c) = a[u];
         *reinterpret_cast<uint4*>(v_pages + off + half + 8 * c) = b[u];
+        if (zero_tail && last_of_sequence(tok_slot, n, (int)gridDim.x, slot))
+          zero_rows_behind<bf16>(v_pages + off + D, page_size - 1 - pos % page_size, D, c, LPH);
         continue;
       }
       dst = k_pages + off;
@@ -498,7 +526,7 @@ __global__ void __launch_bounds__(ROPE_WARPS * 32) qk_norm_rope_store_vec_kernel
 template <int LPH>
 static int launch_vec(const void* qkv, int qkv_stride, const float* wq, const float* wk, const void* cs_table, const int* tok_slot,
                       const int* tok_pos, void* q_out, void* k_pages, void* v_pages, const int* page_table, int max_pages,
-                      int n_tokens, int nH, int nKV, int page_size, float eps, int has_norm, int write_kv, cudaStream_t st) {
+                      int n_tokens, int nH, int nKV, int page_size, float eps, int has_norm, int write_kv, int zero_tail, cudaStream_t st) {
   typedef __nv_bfloat16 bf16;
   const int heads_total = nH + (write_kv ? 2 * nKV : 0);
   const int per_block = ROPE_WARPS * (32 / LPH) * ROPE_VEC_PASSES;
@@ -506,7 +534,7 @@ static int launch_vec(const void* qkv, int qkv_stride, const float* wq, const fl
   if (grid.y > 65535) return DRYFT_ERR_UNSUPPORTED;
   qk_norm_rope_store_vec_kernel<LPH><<<grid, ROPE_WARPS * 32, 0, st>>>(
       (const bf16*)qkv, qkv_stride, wq, wk, (const bf16*)cs_table, tok_slot, tok_pos, (bf16*)q_out, (bf16*)k_pages, (bf16*)v_pages,
-      page_table, max_pages, nH, nKV, page_size, eps, has_norm, write_kv);
+      page_table, max_pages, nH, nKV, page_size, eps, has_norm, write_kv, zero_tail);
   return launch_status();
 }
 
@@ -539,7 +567,7 @@ template <typename T>
 static int launch(const void* qkv, int qkv_stride, const float* wq, const float* wk, const float* inv_freq, const void* cs_table,
                   const int* tok_slot, const int* tok_pos, void* q_out, void* k_pages, void* v_pages,
                   const int* page_table, int max_pages, int n_tokens, int nH, int nKV, int D, int R, int page_size,
-                  float eps, int has_norm, int write_kv, cudaStream_t st) {
+                  float eps, int has_norm, int write_kv, int zero_tail, cudaStream_t st) {
   if (n_tokens <= 0) return 0;
   if (D <= 0 || (R & 1) || R > D || R < 0) return DRYFT_ERR_UNSUPPORTED;
   const int heads_total = nH + (write_kv ? 2 * nKV : 0);
@@ -548,7 +576,7 @@ static int launch(const void* qkv, int qkv_stride, const float* wq, const float*
       !(((uintptr_t)qkv | (uintptr_t)cs_table | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages) & 15) &&
       !(((uintptr_t)wq | (uintptr_t)wk) & 7)) {
 #define DRYFT_ROPE_VEC(L) launch_vec<L>(qkv, qkv_stride, wq, wk, cs_table, tok_slot, tok_pos, q_out, k_pages, v_pages, page_table, \
-                                        max_pages, n_tokens, nH, nKV, page_size, eps, has_norm, write_kv, st)
+                                        max_pages, n_tokens, nH, nKV, page_size, eps, has_norm, write_kv, zero_tail, st)
     return D == 16 ? DRYFT_ROPE_VEC(1) : D == 32 ? DRYFT_ROPE_VEC(2) : D == 64 ? DRYFT_ROPE_VEC(4) : D == 128 ? DRYFT_ROPE_VEC(8) : DRYFT_ROPE_VEC(16);
 #undef DRYFT_ROPE_VEC
   }
@@ -559,18 +587,18 @@ static int launch(const void* qkv, int qkv_stride, const float* wq, const float*
     if (D <= 128)
       qk_norm_rope_store_fast_kernel<T, 1><<<grid, ROPE_WARPS * 32, 0, st>>>(
           (const T*)qkv, qkv_stride, wq, wk, inv_freq, (const T*)cs_table, tok_slot, tok_pos, (T*)q_out, (T*)k_pages,
-          (T*)v_pages, page_table, max_pages, nH, nKV, D, page_size, eps, has_norm, write_kv);
+          (T*)v_pages, page_table, max_pages, nH, nKV, D, page_size, eps, has_norm, write_kv, zero_tail);
     else
       qk_norm_rope_store_fast_kernel<T, 2><<<grid, ROPE_WARPS * 32, 0, st>>>(
           (const T*)qkv, qkv_stride, wq, wk, inv_freq, (const T*)cs_table, tok_slot, tok_pos, (T*)q_out, (T*)k_pages,
-          (T*)v_pages, page_table, max_pages, nH, nKV, D, page_size, eps, has_norm, write_kv);
+          (T*)v_pages, page_table, max_pages, nH, nKV, D, page_size, eps, has_norm, write_kv, zero_tail);
     return launch_status();
   }
   const int head_groups = (heads_total + ROPE_WARPS - 1) / ROPE_WARPS;
   if (head_groups > 65535) return DRYFT_ERR_UNSUPPORTED;
   qk_norm_rope_store_kernel<T><<<dim3((unsigned)n_tokens, (unsigned)head_groups), ROPE_WARPS * 32, 0, st>>>(
       (const T*)qkv, qkv_stride, wq, wk, inv_freq, (const T*)cs_table, tok_slot, tok_pos, (T*)q_out, (T*)k_pages, (T*)v_pages, page_table,
-      max_pages, n_tokens, nH, nKV, D, R, page_size, eps, has_norm, write_kv);
+      max_pages, n_tokens, nH, nKV, D, R, page_size, eps, has_norm, write_kv, zero_tail);
   return launch_status();
 }
 
@@ -578,9 +606,9 @@ DRYFT_API int dryft_qk_norm_rope_store(int is_bf16, const void* qkv, int qkv_str
                                        const float* inv_freq, const void* cs_table, const int* tok_slot, const int* tok_pos, void* q_out,
                                        void* k_pages, void* v_pages, const int* page_table, int max_pages, int n_tokens,
                                        int nH, int nKV, int D, int R, int page_size, float eps, int has_norm,
-                                       int write_kv, cudaStream_t st) {
+                                       int write_kv, int zero_tail, cudaStream_t st) {
   return is_bf16 ? launch<__nv_bfloat16>(qkv, qkv_stride, wq, wk, inv_freq, cs_table, tok_slot, tok_pos, q_out, k_pages, v_pages,
-                                         page_table, max_pages, n_tokens, nH, nKV, D, R, page_size, eps, has_norm, write_kv, st)
+                                         page_table, max_pages, n_tokens, nH, nKV, D, R, page_size, eps, has_norm, write_kv, zero_tail && write_kv, st)
                  : launch<float>(qkv, qkv_stride, wq, wk, inv_freq, cs_table, tok_slot, tok_pos, q_out, k_pages, v_pages,
-                                 page_table, max_pages, n_tokens, nH, nKV, D, R, page_size, eps, has_norm, write_kv, st);
+                                 page_table, max_pages, n_tokens, nH, nKV, D, R, page_size, eps, has_norm, write_kv, zero_tail && write_kv, st);
 }

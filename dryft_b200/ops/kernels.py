@@ -57,7 +57,7 @@ def core() -> ctypes.CDLL:
             lib.dryft_residual_add.argtypes = [_i, _p, _p, _ll, _p]
             lib.dryft_silu_mul.argtypes = [_i, _p, _p, _i, _i, _p]
             lib.dryft_qk_norm_rope_store.argtypes = [_i, _p, _i, _p, _p, _p, _p, _p, _p, _p, _p, _p, _p, _i, _i, _i, _i, _i,
-                                                     _i, _i, _f, _i, _i, _p]
+                                                     _i, _i, _f, _i, _i, _i, _p]
             lib.dryft_rope_table.argtypes = [_i, _p, _p, _p, _i, _i, _p]
             lib.dryft_gemm_nt_f32.argtypes = [_p, _i, _p, _p, _i, _i, _i, _i, _p]
             lib.dryft_argmax_rows.argtypes = [_p, _i, _i, _ll, _p, _p, _p, _p]
@@ -395,8 +395,10 @@ def silu_mul(gate_up, out) -> None:
 # ----------------------------------------------------------------------------- rope + cache write
 def qk_norm_rope_store(qkv, q_norm_w, k_norm_w, inv_freq, tok_slot, tok_pos, q_out, k_pages, v_pages, page_table,
                        n_heads: int, n_kv_heads: int, head_dim: int, rotary_dim: int, eps: float, write_kv: bool = True,
-                       cs_table=None) -> None:
-    """``cs_table`` (from ``rope_table``; optional) holds the step's cos / sin so that layers share them."""
+                       cs_table=None, zero_tail: bool = False) -> None:
+    """``cs_table`` (from ``rope_table``; optional) holds the step's cos / sin so that layers share them.
+    ``zero_tail``: the last token each sequence brings also zeroes the value rows of its page behind its own
+    (what the page's last holder left there), for attention kernels that multiply whole pages."""
     n = qkv.shape[0]
     width = (n_heads + (2 * n_kv_heads if write_kv else 0)) * head_dim
     _need(qkv, "qkv", None, (n, width))
@@ -426,7 +428,7 @@ def qk_norm_rope_store(qkv, q_norm_w, k_norm_w, inv_freq, tok_slot, tok_pos, q_o
                                         _ptr(cs_table), _ptr(tok_slot), _ptr(tok_pos), _ptr(q_out), _ptr(k_pages if write_kv else None),
                                         _ptr(v_pages if write_kv else None), _ptr(page_table if write_kv else None),
                                         max_pages, n, n_heads, n_kv_heads, head_dim, rotary_dim, page_size, float(eps),
-                                        int(has_norm), int(write_kv), _stream()), "qk_norm_rope_store")
+                                        int(has_norm), int(write_kv), int(zero_tail), _stream()), "qk_norm_rope_store")
 
 
 def rope_table(tok_pos, inv_freq, n_tokens: int, dtype: torch.dtype) -> torch.Tensor:

@@ -187,7 +187,8 @@ class Attention:
         K.qk_norm_rope_store(qkv, self.q_norm_w, self.k_norm_w, self.position.inv_freq, ctx.tok_slot, ctx.tok_pos, q,
                              cache.k, cache.v, cache.page_table, self.n_heads, self.n_kv, self.head_dim,
                              self.position.rotary_dim, self.qk_eps, write_kv=owns_cache,
-                             cs_table=table_of(ctx) if table_of is not None else None)
+                             cs_table=table_of(ctx) if table_of is not None else None,
+                             zero_tail=owns_cache and not ctx.decode and (self.use_prefill_tc or self.use_prefill_kernel))
         o = torch.empty((n, self.q_dim), dtype=h.dtype, device=dev)
         if self.use_prefill_tc and not ctx.decode and ctx.n_tiles > 0 and ctx.tile_size <= PREFILL_TILE_TC:
             K.attn_prefill_tc(q, cache.k, cache.v, cache.page_table, ctx.tile_tok0, ctx.tile_rows, ctx.tok_slot, ctx.tok_pos,

@@ -1,5 +1,5 @@
 """The parts of bench.py's contract that need no GPU: more than one GPU is refused with one line and
-exit code 2; the reference arm says why it is unavailable and exits 0; the peaks come from
+exit code 2; without a GPU the reference arm says why it is unavailable and exits 0; the peaks come from
 MEASURED_PEAKS.json when it is there, else the fallback figures."""
 
 import json
@@ -22,7 +22,7 @@ def test_more_than_one_gpu_is_one_line_and_exit_2():
     assert len(lines) == 1 and "one GPU" in lines[0]
 
 
-def test_reference_arm_is_unavailable_with_a_reason():
+def test_reference_arm_without_a_gpu_is_unavailable_with_a_reason():
     r = _run("--impl", "reference", "--gpus", "1", "--steps", "4", "--warmup", "3")
     assert r.returncode == 0
     out = json.loads(r.stdout.strip().splitlines()[-1])

@@ -31,6 +31,13 @@ def _tol(dtype):
     return (2e-2, 2e-2) if dtype == torch.bfloat16 else (2e-5, 2e-5)
 
 
+# bfloat16 attention outputs: two bfloat16 ulps of the result (its own rounding, and the rounding of P before
+# the second product, kernels/attn_decode.py:12-14,89, which moves a sum of n weighted values by less than one
+# ulp of the largest) plus a small absolute term for outputs near zero.  One key dropped among a hundred moves
+# an output by about 1e-2: outside.  (tests/test_gpu_attention_keys.py has the tests no single key can pass.)
+ATTN_BF16_TOL = dict(rtol=2.0 ** -7, atol=3e-3)
+
+
 # ------------------------------------------------------------------------------------ metadata
 def test_step_meta_and_advance():
     k = K()
@@ -437,7 +444,7 @@ def test_attn_rows(dtype, n_heads, n_kv, d, window):
     ref = torch.stack([
         _attn_ref(q[i], seqs[s][0], seqs[s][1], p, scale, window) if s >= 0 else torch.zeros(n_heads * d)
         for i, (s, p) in enumerate(rows)])
-    rt, at = _tol(dtype)
+    rt, at = (ATTN_BF16_TOL["rtol"], ATTN_BF16_TOL["atol"]) if dtype == torch.bfloat16 else _tol(dtype)
     for splits in (1, 3, 8):
         out = torch.full((n, n_heads * d), 9.0, device=DEV).to(dtype)
         part_o = torch.empty(n, n_heads, splits, d, device=DEV) if splits > 1 else None
@@ -508,7 +515,7 @@ def test_attn_decode_fused(n_heads, n_kv, d, rot, window):
             continue
         run()
         assert torch.isfinite(out.float()).all()
-        torch.testing.assert_close(out.cpu().float(), ref, rtol=2e-2, atol=2e-2)
+        torch.testing.assert_close(out.cpu().float(), ref, **ATTN_BF16_TOL)
         changed_k = (kc != kc0).any(dim=-1)
         changed_v = (vc != vc0).any(dim=-1)
         assert int(changed_k.sum()) == 5 * n_kv and int(changed_v.sum()) == 5 * n_kv  # one row per live token and kv head
@@ -586,7 +593,7 @@ def test_attn_prefill(n_heads, n_kv, d, window):
     k.attn_prefill(q_all, kc, vc, pt, i32(tiles0), i32(tilesn), i32(tok_slot), i32(tok_pos), out, len(tiles0), scale, window)
     ref = torch.stack(refs)
     assert torch.isfinite(out.float()).all()
-    torch.testing.assert_close(out.cpu().float(), ref, rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(out.cpu().float(), ref, **ATTN_BF16_TOL)
 
 
 @pytest.mark.parametrize("n_heads,n_kv,d", [(8, 2, 128), (3, 3, 64), (4, 1, 128)])
@@ -625,7 +632,7 @@ def test_attn_prefill_tc(n_heads, n_kv, d, window):
     torch.cuda.synchronize()
     k.check_error_flags()
     assert torch.isfinite(out.float()).all()
-    torch.testing.assert_close(out.cpu().float(), torch.stack(refs), rtol=2e-2, atol=2e-2)
+    torch.testing.assert_close(out.cpu().float(), torch.stack(refs), **ATTN_BF16_TOL)
 
 
 @pytest.mark.parametrize("where", ["early", "late", "steps"])

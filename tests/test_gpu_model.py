@@ -561,18 +561,18 @@ def test_layer_reading_another_layers_cache():
             out = eng.generate_many([toks[:50], toks[:9]], max_new_tokens=12)
             with torch.inference_mode():
                 for prompt, got in zip((toks[:50], toks[:9]), out):
+                    # our tokens fed back by hand, one sequence alone: each must be the best choice of that step's
+                    # logits -- exactly in 32-bit, up to the measured bfloat16 noise of these logits otherwise
                     s = eng.cache.open_sequences(1)
                     lg = eng.stepper.step(s, [prompt], [[len(prompt) - 1]])
-                    want = []
-                    for _ in range(12):
-                        nxt = int(lg[0].argmax())
-                        want.append(nxt)
-                        lg = eng.stepper.step(s, [[nxt]], [[0]])
+                    for t in got:
+                        margin = float(lg[0].max() - lg[0][t])
+                        if dtype == "float32":
+                            assert margin <= 2 * H.FP32_TOL * float(lg.abs().max()), f"token {t} is not the 32-bit choice"
+                        else:
+                            assert margin <= tol * float(lg.abs().max()), f"token {t} loses {margin:.3g} to the best"
+                        lg = eng.stepper.step(s, [[t]], [[0]])
                     eng.cache.close_sequences(s)
-                    if dtype == "float32":
-                        assert list(got) == want
-                    else:
-                        assert list(got)[:3] == want[:3]   # later tokens may part at a near tie in bfloat16
             del eng
     finally:
         unregister_architecture("SharedKVForCausalLM")

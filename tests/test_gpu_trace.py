@@ -41,7 +41,7 @@ def compare(got: np.ndarray, name, tokens, rows, model_dirs, dtype, what):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["a", "b", "c"])
+@pytest.mark.parametrize("name", ["a", "b", "c", "d"])
 def test_trace_replay_every_way_of_cutting(model_dirs, tmp_path, name, dtype):
     lengths = [40, 97, 33, 150, 64, 71]
     reqs = [H.prompts_for(name, [n], seed=200 + i)[0] for i, n in enumerate(lengths)]

@@ -80,5 +80,9 @@ def test_static_scratch_entry_point_matches_the_ordinary_one(dtype):
     rc = fn(int(dtype == torch.bfloat16), _ptr(q), _ptr(kc), _ptr(vc), _ptr(pt), pt.shape[1], _ptr(slot), _ptr(pos),
             _ptr(untouched), big_rows, n_kv, splits, scale, 0, stream)
     assert rc == SCRATCH_TOO_SMALL
+    # counts whose product would wrap around 64 bits are refused too (the check divides, it does not multiply)
+    rc = fn(int(dtype == torch.bfloat16), _ptr(q), _ptr(kc), _ptr(vc), _ptr(pt), pt.shape[1], _ptr(slot), _ptr(pos),
+            _ptr(untouched), 2**31 - 1, 65535, 65535, scale, 0, stream)
+    assert rc == SCRATCH_TOO_SMALL
     torch.cuda.synchronize()
     assert float(untouched[0]) == 3.0
