@@ -12,7 +12,8 @@ head) with random weights, a batch of 8 sequences with 512-token prompts, and ti
             list out per step (every step copies its slot list host->device from pinned memory and
             reads the chosen tokens device->host)
   prefill   one 2,048-token prompt through the step function: tokens a second, ms, and the step's
-            flops / time / the bf16 peak
+            flops / time / the bf16 peak of a product timed alone (the step is timed alone too)
+  spread, peak_mem_gib   (slowest - fastest) / median over the eighths of the timed region; the allocator's peaks
   roofline  the decode step against HBM: bytes it has to read (every weight once, and the cache of
             the live requests) / its time, against the measured copy bandwidth
   points    decode tokens a second at batch 1 and 64
@@ -47,11 +48,13 @@ FALLBACK_BF16_TFLOPS = 1590.0
 
 
 def peaks():
+    """(copy bandwidth GB/s, bf16 TFLOP/s of a product timed alone, source).  The prefill step is timed alone between
+    synchronisations, so its fraction is taken against the burst figure, not the one sustained under the power cap."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.isfile(path):
         try:
             p = json.load(open(path))
-            return float(p["hbm_gbs"]), float(p.get("bf16_tflops_sustained") or p["bf16_tflops"]), "measured"
+            return float(p["hbm_gbs"]), float(p["bf16_tflops"]), "measured"
         except Exception:
             pass
     return FALLBACK_HBM_GBS, FALLBACK_BF16_TFLOPS, "fallback"
@@ -124,17 +127,24 @@ def decode_device_time(eng, batch, prompt_len, steps, warmup, seed):
             torch.cuda.synchronize()
             n0 = K.launch_count
             ctx0 = eng.cache.len_host[slots[0]]
-            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            start.record()
-            for _ in range(steps):
+            # one event every `every` steps: the whole region gives the time, the pieces give its spread
+            every = max(1, steps // 8)
+            marks = [torch.cuda.Event(enable_timing=True)]
+            marks[0].record()
+            for i in range(steps):
                 one()
-            end.record()
+                if (i + 1) % every == 0 or i + 1 == steps:
+                    marks.append(torch.cuda.Event(enable_timing=True))
+                    marks[-1].record()
             torch.cuda.synchronize()
-            ms = start.elapsed_time(end) / steps
+            ms = marks[0].elapsed_time(marks[-1]) / steps
+            pieces = [a.elapsed_time(b) / every for a, b in zip(marks[:-1], marks[1:])][: steps // every]
+            spread = (max(pieces) - min(pieces)) / statistics.median(pieces) if len(pieces) > 1 else 0.0
             launches = K.launch_count - n0
             ctx1 = eng.cache.len_host[slots[0]]
         finally:
             eng.cache.close_sequences(slots)
+    decode_device_time.spread = spread
     return ms, launches, (ctx0 + ctx1) / 2.0
 
 
@@ -388,6 +398,7 @@ def main() -> int:
     ms, launches, mean_ctx = decode_device_time(eng, args.batch, args.prompt_len, args.steps, warmup, args.seed)
     clock_info = clocks.stop()
     value = args.batch * 1000.0 / ms
+    spread = decode_device_time.spread
 
     e2e, h2d, d2h = decode_e2e(eng, args.batch, args.prompt_len, args.steps, args.seed + 1)
 
@@ -423,6 +434,10 @@ def main() -> int:
         },
         "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches,
+        # as hari495/dryft's harness reports them (agent/bench.py:58-59,86-87): (slowest - fastest) / median over the
+        # eighths of the timed region, and the allocator's peaks over the whole run (weights, cache for batch 64, prompts)
+        "spread": spread,
+        "peak_mem_gib": {"allocated": torch.cuda.max_memory_allocated() / 2**30, "reserved": torch.cuda.max_memory_reserved() / 2**30},
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm_gbs, "unit": "GB/s", "frac": achieved / hbm_gbs},
         "points": points,

@@ -21,7 +21,7 @@ every position); the host copy is what reservations are decided from.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Dict, List, Optional, Sequence, Tuple
+from typing import Dict, List, Mapping, Optional, Sequence, Tuple
 
 import torch
 
@@ -40,7 +40,9 @@ class KVNeed:
 
 @dataclass(frozen=True)
 class StateNeed:
-    """Fixed-size state per sequence, zeroed when a sequence starts."""
+    """Fixed-size state per sequence, zeroed when a sequence starts.  A mixer that keeps several kinds of
+    state (a short convolution's tail and a recurrent state, say) asks with a mapping ``{name: StateNeed}``
+    and is handed ``{name: tensor}``."""
 
     shape: Tuple[int, ...]
     dtype: torch.dtype
@@ -123,7 +125,14 @@ class SequenceCache:
             if kv is not None:
                 by_need.setdefault(kv, []).append(i)
             if st is not None:
-                self._states[i] = torch.zeros((max_slots, *st.shape), dtype=st.dtype, device=device)
+                make = lambda need: torch.zeros((max_slots, *need.shape), dtype=need.dtype, device=device)
+                if isinstance(st, StateNeed):
+                    self._states[i] = make(st)
+                elif isinstance(st, Mapping) and st and all(isinstance(v, StateNeed) for v in st.values()):
+                    self._states[i] = {name: make(need) for name, need in st.items()}
+                else:
+                    raise CacheError(f"run step {i}: state_need() must give a StateNeed or a mapping of names to StateNeed, "
+                                     f"got {st!r}")
         for need, steps in by_need.items():
             g = _KVGroup(need, steps, n_pages, page_size, max_slots, max_pages_per_slot, dtype, device)
             for j, s in enumerate(steps):
@@ -144,8 +153,16 @@ class SequenceCache:
         g = self._groups[loc[0]]
         return CacheEntry(g.k[loc[1]], g.v[loc[1]], g.page_table, self.page_size, g.need.window)
 
-    def state(self, run_step: int) -> Optional[torch.Tensor]:
+    def state(self, run_step: int):
+        """The run step's state ``[slots, *shape]`` (a mapping of such tensors if it asked with a mapping), or None."""
         return self._states.get(run_step)
+
+    def _state_tensors(self) -> List[torch.Tensor]:
+        seen: Dict[int, torch.Tensor] = {}
+        for st in self._states.values():
+            for t in (st.values() if isinstance(st, dict) else (st,)):
+                seen[id(t)] = t
+        return list(seen.values())
 
     def n_groups(self) -> int:
         return len(self._groups)
@@ -171,7 +188,7 @@ class SequenceCache:
             idx = torch.tensor(slots, dtype=torch.int64).to(self.device, non_blocking=True)
             self.seq_len.index_fill_(0, idx, 0)
             self.last_token.index_fill_(0, idx, 0)
-            for st in {id(t): t for t in self._states.values()}.values():
+            for st in self._state_tensors():
                 st.index_fill_(0, idx, 0)
         return slots
 

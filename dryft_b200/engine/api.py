@@ -50,6 +50,10 @@ class EngineOptions:
     pdl: bool = True                       # programmatic dependent launch between the decode products
     norm_ahead: bool = True                # fused decode: the next norm's weight is applied by the product before it
     tcgen05: bool = True                   # prefill attention on tcgen05 / TMEM / TMA where the head size allows
+    # Prompts longer than this go through the step function in chunks of this many tokens per sequence (the same
+    # step again, from the cache the chunk before left): bounds the step's activations ([tokens, q + 2 kv], the
+    # attention output) whatever the prompt length.  None: whole prompts in one step.
+    prefill_chunk_tokens: Optional[int] = None
 
 
 def _require_cuda(device: str) -> torch.device:
@@ -75,8 +79,14 @@ class Engine:
 
     @classmethod
     def from_config(cls, config: Union[Mapping[str, Any], Any], seed: int = 0, std: float = 0.02,
-                    options: Optional[EngineOptions] = None, **kw: Any) -> "Engine":
-        """Random weights made on the device, no model folder (for benchmarks of large shapes)."""
+                    options: Optional[EngineOptions] = None, draw_on: str = "device", **kw: Any) -> "Engine":
+        """Random weights without a model folder.  ``draw_on="device"`` draws them with the GPU's generator
+        (seconds for billions of values: benchmarks of large shapes); ``draw_on="cpu"`` draws them with the CPU's
+        generator, tensor by tensor -- exactly the tensors ``write_random_model(config, seed, ...)`` stores, so a
+        seed then names one model whether it is written to a folder or built here.  The two generators give
+        different values for the same seed."""
+        if draw_on not in ("device", "cpu"):
+            raise ValueError(f"draw_on must be 'device' or 'cpu', got {draw_on!r}")
         self = cls.__new__(cls)
         opts = options or EngineOptions(**kw)
         cfg = config_from_dict(config) if isinstance(config, Mapping) else config
@@ -85,12 +95,16 @@ class Engine:
         dtype = _DTYPES[opts.dtype]
         exp = expected_tensors(spec)
         skip = [n for n, info in exp.items() if info.optional]
-        self._build(cfg, spec, RandomSource(exp, seed, dtype, dev, std=std, skip=skip), opts, dev, dtype)
+        source = RandomSource(exp, seed, dtype, dev, std=std, skip=skip,
+                              draw_device=torch.device("cpu") if draw_on == "cpu" else dev)
+        self._build(cfg, spec, source, opts, dev, dtype)
         return self
 
     def _build(self, config, spec, source, opts: EngineOptions, dev: torch.device, dtype: torch.dtype) -> None:
         torch.backends.cuda.matmul.allow_tf32 = False  # engine/engine.py:32-33
         torch.backends.cudnn.allow_tf32 = False
+        if opts.prefill_chunk_tokens is not None and opts.prefill_chunk_tokens <= 0:
+            raise ValueError(f"prefill_chunk_tokens must be positive, got {opts.prefill_chunk_tokens}")
         self.config = config
         self.spec = spec
         self.options = opts
@@ -172,9 +186,29 @@ class _DeviceBackend:
     def _ints(self, vals: Sequence[int]) -> torch.Tensor:
         return torch.tensor(list(vals), dtype=torch.int32).to(self.e.device, non_blocking=True)
 
+    def _prompt_logits(self, handles, prompts) -> torch.Tensor:
+        """Logits at each prompt's last token: one step, or the same step chunk after chunk."""
+        e = self.e
+        chunk = e.options.prefill_chunk_tokens
+        longest = max(len(p) for p in prompts)
+        if not chunk or longest <= chunk:
+            return e.stepper.step(handles, prompts, [[len(p) - 1] for p in prompts])
+        rows: List[Optional[torch.Tensor]] = [None] * len(prompts)
+        for c0 in range(0, longest, chunk):
+            live = [b for b, p in enumerate(prompts) if len(p) > c0]      # shorter prompts are done already
+            pieces = [prompts[b][c0:c0 + chunk] for b in live]
+            ends = [len(prompts[b]) <= c0 + chunk for b in live]          # this piece holds the prompt's last token
+            out = e.stepper.step([handles[b] for b in live], pieces, [[len(pc) - 1] if end else [] for pc, end in zip(pieces, ends)])
+            at = 0
+            for b, end in zip(live, ends):
+                if end:
+                    rows[b] = out[at:at + 1]
+                    at += 1
+        return torch.cat(rows)
+
     def prefill(self, handles, prompts, seq_ids, params: SamplingParams) -> List[int]:
         e = self.e
-        logits = e.stepper.step(handles, prompts, [[len(p) - 1] for p in prompts])
+        logits = self._prompt_logits(handles, prompts)
         chosen = choose(logits, params, row_seq=self._ints(seq_ids), step=0, row_slot=self._ints(handles),
                         last_token=e.cache.last_token)
         self.h2d_bytes += 4 * (sum(len(p) for p in prompts) + 4 * len(prompts))

@@ -299,8 +299,25 @@ def error_flag(device: torch.device) -> torch.Tensor:
     return _error_flags[idx]
 
 
+_watched: list = []   # (weak reference to a device int32 flag, what a raised flag means)
+
+
+def watch_flag(flag: torch.Tensor, what: str) -> None:
+    """Have ``check_error_flags`` read this device flag too (a part's own error flag, e.g. the embedding's)."""
+    import weakref
+
+    _watched.append((weakref.ref(flag), what))
+
+
 def check_error_flags() -> None:
-    """Raise if any kernel gave up a bounded wait since the last check (reads the flag: a sync)."""
+    """Raise if any kernel gave up a bounded wait, or a part's watched flag was raised, since the last check
+    (reads the flags: a sync)."""
+    _watched[:] = [(ref, what) for ref, what in _watched if ref() is not None]
+    for ref, what in _watched:
+        flag = ref()
+        if flag is not None and int(flag.item()) != 0:
+            flag.zero_()
+            raise KernelError(what)
     for idx, flag in _error_flags.items():
         code = int(flag.item())
         if code != 0:

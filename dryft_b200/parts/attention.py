@@ -22,7 +22,7 @@ import torch
 from ..cache.store import CacheEntry, KVNeed, StateNeed
 from ..config.spec import PartSpec
 from ..ops import kernels as K
-from .base import NORMS, POSITIONS, Runtime, StepContext, TensorInfo, register_mixer
+from .base import NORMS, POSITIONS, Runtime, StepContext, TensorInfo, fused_rms, register_mixer
 from .linear import linear, weighted_for
 
 PREFILL_TILE = 64      # query rows per block of the mma.sync prefill kernel
@@ -129,7 +129,7 @@ class Attention:
         """Few rows, bfloat16 everywhere, widths the weight-streaming product takes."""
         rt = self.rt
         return (rt.fuse_decode and rt.is_bf16 and n_rows <= min(rt.small_m_max, K.SMALL_M_LIMIT)
-                and type(norm).__name__ == "RMSNorm" and self.w_qkv.dtype == torch.bfloat16
+                and fused_rms(norm) is not None and self.w_qkv.dtype == torch.bfloat16
                 and self.w_o.dtype == torch.bfloat16 and self.hidden % 16 == 0 and self.q_dim % 16 == 0)
 
     weighted_ahead = True   # forward_normed takes ``xw`` / ``next_norm`` and returns the weighted stream too
@@ -143,17 +143,18 @@ class Attention:
         n = x.shape[0]
         w = self.w_qkv if owns_cache else self.w_qkv[: self.q_dim]
         qkv = torch.empty((n, w.shape[0]), dtype=x.dtype, device=x.device)
+        norm_w, eps = fused_rms(norm)
         if xw is not None and K.weighted_ahead_supported(self.hidden):
-            K.gemm_small_m(x, w, qkv, xw_in=xw, norm_w=norm.weight, ss_in=ss, ss_parts=ss_parts, eps=norm.eps, pdl=self.rt.pdl)
+            K.gemm_small_m(x, w, qkv, xw_in=xw, norm_w=norm_w, ss_in=ss, ss_parts=ss_parts, eps=eps, pdl=self.rt.pdl)
         else:
-            K.gemm_small_m(x, w, qkv, norm_w=norm.weight, ss_in=ss, ss_parts=ss_parts, eps=norm.eps, pdl=self.rt.pdl)
+            K.gemm_small_m(x, w, qkv, norm_w=norm_w, ss_in=ss, ss_parts=ss_parts, eps=eps, pdl=self.rt.pdl)
         o = self._attend(qkv, ctx, cache, owns_cache)
         parts = (self.hidden + 15) // 16
         ss_out = torch.empty(parts * K.SS_STRIDE, dtype=torch.float32, device=x.device)
         xw_out = None
         if weighted_for(next_norm, self.hidden, self.q_dim, self.rt):
             xw_out = torch.empty_like(x)
-            K.gemm_small_m(o, self.w_o, x, mode="residual", ss_out=ss_out, pdl=self.rt.pdl, next_w=next_norm.weight, xw_out=xw_out)
+            K.gemm_small_m(o, self.w_o, x, mode="residual", ss_out=ss_out, pdl=self.rt.pdl, next_w=fused_rms(next_norm)[0], xw_out=xw_out)
         else:
             K.gemm_small_m(o, self.w_o, x, mode="residual", ss_out=ss_out, pdl=self.rt.pdl)
         return ss_out, parts, xw_out

@@ -8,6 +8,8 @@ Interfaces
 norm        ``tensors(params, prefix)``; ``__init__(params, prefix, weights, rt)``;
             ``forward(x, out=None)``; ``add_forward(x, delta, rows=None)`` -> normed rows, with
             ``x += delta`` written back (fused residual add, ``kernels/rmsnorm.py:21-39``).
+            Optional: ``rms_params() -> (weight, eps)`` declares the plain RMS arithmetic, which lets the
+            decode products fold the norm into themselves (``fused_rms`` below).
 position    ``__init__(params, head_dim, rt)``; gives ``rotary_dim`` and ``inv_freq`` to the mixer.
 mixer       ``tensors``; ``__init__``; ``kv_need()`` / ``state_need()``;
             ``forward(h, ctx, cache, state, owns_cache)`` -> ``[tokens, hidden]`` (not yet added).
@@ -96,6 +98,23 @@ class Residual:
     # product for the product behind that norm, which then has no prologue (it scales its sums instead)
     xw: Optional[torch.Tensor] = None
     xw_norm: Optional[Any] = None
+
+
+def fused_rms(norm) -> Optional[Tuple[torch.Tensor, float]]:
+    """``(weight, eps)`` if ``norm`` declares, through a method ``rms_params()``, that it computes exactly
+    ``weight * cast(x32 * rsqrt(mean(x32^2) + eps))`` with a 32-bit ``weight`` -- the arithmetic the fused decode
+    products fold into themselves -- else None.  A norm of any other arithmetic (a ``1 + w`` weight, a bias, a
+    mean subtracted) simply does not offer the method, whatever its class is called, and is run as its own kernel."""
+    get = getattr(norm, "rms_params", None)
+    if not callable(get):
+        return None
+    params = get()
+    if params is None:
+        return None
+    weight, eps = params
+    if not isinstance(weight, torch.Tensor) or weight.dtype != torch.float32 or weight.dim() != 1:
+        return None
+    return weight, float(eps)
 
 
 class Registry:

@@ -18,7 +18,7 @@ from typing import Optional, Tuple
 import torch
 
 from ..ops import kernels as K
-from .base import Residual, StepContext, register_block
+from .base import Residual, StepContext, fused_rms, register_block
 from .linear import weighted_for
 
 
@@ -54,7 +54,7 @@ class PreNormBlock:
                 ss = torch.empty(K.SS_STRIDE, dtype=torch.float32, device=x.device)
                 if ahead_m and weighted_for(self.norm_mixer, x.shape[1], x.shape[1], self.mixer.rt):
                     xw = torch.empty_like(x)
-                    K.row_sumsq(x, ss, norm_w=self.norm_mixer.weight, xw_out=xw)
+                    K.row_sumsq(x, ss, norm_w=fused_rms(self.norm_mixer)[0], xw_out=xw)
                 else:
                     K.row_sumsq(x, ss)
                 parts = 1

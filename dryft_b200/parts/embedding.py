@@ -12,7 +12,7 @@ from typing import Dict, Mapping, Optional
 import torch
 
 from ..ops import kernels as K
-from .base import Runtime, TensorInfo, register_embedding, register_head
+from .base import Runtime, TensorInfo, fused_rms, register_embedding, register_head
 from .linear import linear
 
 
@@ -27,7 +27,10 @@ class Embedding:
         self.vocab = int(params["vocab_size"])
         self.hidden = int(params["hidden_size"])
         self.table = weights.load(prefix + "weight", "table")
+        # raised by the gather for an id outside the table (its row is zeroed, not read); read with the other
+        # device flags by ``kernels.check_error_flags``
         self.err = torch.zeros(1, dtype=torch.int32, device=rt.device)
+        K.watch_flag(self.err, "a token id outside the embedding table reached the embedding gather (its row was zeroed)")
 
     def forward(self, tokens: torch.Tensor, n_rows: int) -> torch.Tensor:
         out = torch.empty((n_rows, self.hidden), dtype=self.table.dtype, device=self.table.device)
@@ -69,15 +72,16 @@ class LMHead:
     def can_fuse(self, n_rows: int, norm) -> bool:
         rt = self.rt
         return (rt.fuse_decode and rt.is_bf16 and n_rows <= min(rt.small_m_max, K.SMALL_M_LIMIT)
-                and type(norm).__name__ == "RMSNorm" and self.weight.dtype == torch.bfloat16
+                and fused_rms(norm) is not None and self.weight.dtype == torch.bfloat16
                 and self.weight.shape[1] % 16 == 0)
 
     def forward_normed(self, x: torch.Tensor, ss, ss_parts: int, norm, xw=None) -> torch.Tensor:
         """Logits of every row of ``x`` with the final norm inside the product (decode); ``xw``: ``x``
         weighted by the final norm's weight already."""
         out = torch.empty((x.shape[0], self.vocab), dtype=torch.float32, device=x.device)
+        norm_w, eps = fused_rms(norm)
         if xw is not None and K.weighted_ahead_supported(x.shape[1]):
-            K.gemm_small_m(x, self.weight, out, xw_in=xw, norm_w=norm.weight, ss_in=ss, ss_parts=ss_parts, eps=norm.eps, pdl=self.rt.pdl)
+            K.gemm_small_m(x, self.weight, out, xw_in=xw, norm_w=norm_w, ss_in=ss, ss_parts=ss_parts, eps=eps, pdl=self.rt.pdl)
         else:
-            K.gemm_small_m(x, self.weight, out, norm_w=norm.weight, ss_in=ss, ss_parts=ss_parts, eps=norm.eps, pdl=self.rt.pdl)
+            K.gemm_small_m(x, self.weight, out, norm_w=norm_w, ss_in=ss, ss_parts=ss_parts, eps=eps, pdl=self.rt.pdl)
         return out

@@ -17,7 +17,7 @@ from typing import Optional
 import torch
 
 from ..ops import kernels as K
-from .base import Runtime
+from .base import Runtime, fused_rms
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, rt: Runtime, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
@@ -53,6 +53,6 @@ def weighted_for(next_norm, width: int, k_in: int, rt: Runtime) -> bool:
     """Whether a fused decode product of ``k_in`` inputs that updates a stream of ``width`` should also leave
     the stream weighted for ``next_norm`` (an RMS norm over ``width``): both it and the product behind that
     norm must be of the form compiled per inner size."""
-    return (next_norm is not None and rt.norm_ahead and rt.is_bf16 and type(next_norm).__name__ == "RMSNorm"
-            and getattr(next_norm, "weight", None) is not None and next_norm.weight.numel() == width
+    rms = fused_rms(next_norm) if next_norm is not None else None
+    return (rms is not None and rt.norm_ahead and rt.is_bf16 and rms[0].numel() == width
             and K.weighted_ahead_supported(width) and K.weighted_ahead_supported(k_in))

@@ -26,6 +26,10 @@ class RMSNorm:
         self.rt = rt
         self.weight = weights.load(prefix + "weight", "vector")  # float32 [size]
 
+    def rms_params(self):
+        """This norm is ``weight * cast(x32 * rsqrt(mean(x32^2) + eps))``: products may fold it into themselves."""
+        return self.weight, self.eps
+
     def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None, n_rows: Optional[int] = None) -> torch.Tensor:
         n = n_rows if n_rows is not None else (rows.numel() if rows is not None else x.shape[0])
         out = torch.empty((n, self.size), dtype=x.dtype, device=x.device)

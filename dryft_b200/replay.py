@@ -41,7 +41,7 @@ def main(argv=None) -> int:
     from .engine.api import Engine, EngineOptions
     from .ops import kernels
 
-    page = 64
+    page = EngineOptions().page_size   # requests are counted in the cache's own unit
     n_tokens = max(page, (args.max_tokens + page - 1) // page * page)
     opts = EngineOptions(dtype=args.dtype, max_batch=min(n_tokens // page, 4096), max_seq_len=n_tokens,
                          max_tokens=n_tokens, page_size=page, cuda_graphs=False)

@@ -103,11 +103,15 @@ def random_tensor(name: str, info: TensorInfo, seed: int, std: float, device: to
 
 
 class RandomSource(WeightSource):
-    """Random weights made directly on the device (no model folder), values rounded to
-    ``store_dtype`` first as a checkpoint would hold them."""
+    """Random weights without a model folder, values rounded to ``store_dtype`` first as a checkpoint
+    would hold them."""
 
     def __init__(self, expected: Mapping[str, TensorInfo], seed: int, engine_dtype: torch.dtype, device: torch.device,
-                 std: float = 0.02, store_dtype: torch.dtype = torch.bfloat16, skip: Sequence[str] = ()):
+                 std: float = 0.02, store_dtype: torch.dtype = torch.bfloat16, skip: Sequence[str] = (),
+                 draw_device: Optional[torch.device] = None):
+        # the generator the values come from: the device's by default; the CPU's gives the very tensors that
+        # ``write_random_model`` stores for the same seed (the two generators differ)
+        self.draw_device = draw_device if draw_device is not None else device
         self.expected = dict(expected)
         self.seed = seed
         self.std = std
@@ -123,4 +127,4 @@ class RandomSource(WeightSource):
         return self.store_dtype
 
     def _read(self, name: str) -> torch.Tensor:
-        return random_tensor(name, self.expected[name], self.seed, self.std, self.device).to(self.store_dtype)
+        return random_tensor(name, self.expected[name], self.seed, self.std, self.draw_device).to(self.store_dtype)

@@ -170,6 +170,33 @@ def test_state_is_zeroed_when_a_slot_is_reused():
     assert s2 == s and float(st[s].abs().max()) == 0.0 and int(c.seq_len[s]) == 0 and int(c.last_token[s]) == 0
 
 
+def test_a_mixer_may_ask_for_several_named_states():
+    """A mapping of names to ``StateNeed`` gives a mapping of tensors of their own shapes and dtypes, all zeroed
+    when the slot is taken again; a borrower shares them; anything else is refused."""
+    import pytest
+
+    from dryft_b200.cache.slots import CacheError
+
+    two = {"tail": StateNeed((3, 5), torch.bfloat16), "h": StateNeed((4,), torch.float32)}
+    c = SequenceCache([(None, two), (KVNeed(2, 16, None), None), (None, None)], [None, None, 0], max_tokens=256, max_slots=2,
+                      max_seq_len=128, page_size=64, dtype=torch.float32, device=torch.device("cpu"))
+    st = c.state(0)
+    assert set(st) == {"tail", "h"} and st["tail"].shape == (2, 3, 5) and st["tail"].dtype == torch.bfloat16
+    assert st["h"].shape == (2, 4) and st["h"].dtype == torch.float32
+    assert c.state(2) is st and c.state(1) is None
+    a, b = c.open_sequences(2)
+    st["tail"][a] = 1.0
+    st["h"][a] = 2.0
+    st["h"][b] = 3.0
+    c.close_sequences([a])
+    (a2,) = c.open_sequences(1)
+    assert a2 == a and float(st["tail"][a].abs().max()) == 0.0 and float(st["h"][a].abs().max()) == 0.0
+    assert float(st["h"][b].min()) == 3.0          # the other sequence's state is untouched
+    with pytest.raises(CacheError):
+        SequenceCache([(None, {"x": 3})], [None], max_tokens=64, max_slots=1, max_seq_len=64, page_size=64,
+                      dtype=torch.float32, device=torch.device("cpu"))
+
+
 def _random_traffic(device):
     rng = random.Random(1)
     c = _cache(window=40, max_tokens=1024, slots=3, device=device)
