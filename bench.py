@@ -347,6 +347,8 @@ def main() -> int:
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--small-m-max", type=int, default=None,
                     help="rows up to which decode products stream weights themselves (the engine's default if not given)")
+    ap.add_argument("--engine-opt", action="append", default=[], metavar="NAME=VALUE",
+                    help="an EngineOptions switch for an A/B run, e.g. norm_ahead=0, pdl=0, fuse_decode=0 (named in config)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -370,10 +372,14 @@ def main() -> int:
     # the full run also measures batch 64; a single phase holds only what its batch needs (long contexts fit)
     max_batch = max(64, args.batch) if args.phase == "all" else args.batch
     ctx_cap = args.prompt_len + args.steps + warmup + 64
+    engine_opts = {}
+    for item in args.engine_opt:
+        name, _, val = item.partition("=")
+        engine_opts[name] = {"0": False, "1": True}.get(val, int(val) if val.lstrip("-").isdigit() else val)
     eng = Engine.from_config(cfg, seed=args.seed, dtype="bfloat16", max_batch=max_batch,
                              max_seq_len=max(raw["max_position_embeddings"], 2048 + 64, ctx_cap),
                              max_tokens=max(max_batch * (ctx_cap + 64), 4096),
-                             **({"small_m_max": args.small_m_max} if args.small_m_max is not None else {}))
+                             **({"small_m_max": args.small_m_max} if args.small_m_max is not None else {}), **engine_opts)
     torch.cuda.synchronize()
 
     if args.phase == "prefill":
@@ -430,7 +436,7 @@ def main() -> int:
             "tied_head": cfg.tie_word_embeddings, "global_batch": args.batch, "seq_len": args.prompt_len,
             "mean_context": mean_ctx, "max_context": raw["max_position_embeddings"], "page_size": 64,
             "parallelism": "single-gpu", "cuda_graphs": True, "l2": "inputs>L2 (8 GB of weights per step)",
-            "peaks": peak_src,
+            "peaks": peak_src, **({"engine_opts": ",".join(args.engine_opt)} if args.engine_opt else {}),
         },
         "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": launches,
