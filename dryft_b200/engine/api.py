@@ -45,7 +45,9 @@ class EngineOptions:
     page_size: int = 64
     cuda_graphs: bool = True
     device: str = "cuda:0"
-    small_m_max: int = 8                   # rows up to which decode products stream weights themselves (cuBLAS above)
+    small_m_max: int = 8                   # rows up to which decode products stream weights through registers (mma.sync)
+    stream_m_max: int = 0                  # rows up to which they stream them by TMA into tcgen05.mma above that (0: cuBLAS,
+                                           # which is faster today: profiles/gemm_stream_microbench.md)
     fuse_decode: bool = True               # fold norms, adds and SiLU*mul into the decode products
     pdl: bool = True                       # programmatic dependent launch between the decode products
     norm_ahead: bool = True                # fused decode: the next norm's weight is applied by the product before it
@@ -112,7 +114,7 @@ class Engine:
         self.dtype = dtype
         props = torch.cuda.get_device_properties(dev)
         self.rt = Runtime(dtype=dtype, device=dev, page_size=opts.page_size, sm_count=props.multi_processor_count,
-                          small_m_max=opts.small_m_max, fuse_decode=opts.fuse_decode, pdl=opts.pdl, tcgen05=opts.tcgen05, norm_ahead=opts.norm_ahead)
+                          small_m_max=opts.small_m_max, stream_m_max=opts.stream_m_max, fuse_decode=opts.fuse_decode, pdl=opts.pdl, tcgen05=opts.tcgen05, norm_ahead=opts.norm_ahead)
         with torch.cuda.device(dev), torch.no_grad():
             self.model = DecoderModel(spec, source, self.rt)
             self.max_seq_len = opts.max_seq_len or min(spec.max_positions, 8192)

@@ -116,17 +116,36 @@ _gemm_stream: Optional[ctypes.CDLL] = None
 
 
 def gemm_stream_lib() -> ctypes.CDLL:
-    """The weight-streaming decode product on tcgen05 / TMEM / TMA with cluster split-K."""
+    """The weight-streaming decode product for up to 64 rows on tcgen05 / TMEM / TMA, work cut evenly over the SMs."""
     global _gemm_stream
     with _lock:
         if _gemm_stream is None:
             lib = _load(build.build_library("gemm_stream", ("gemm_stream.cu",)))
-            lib.dryft_gemm_stream.argtypes = [_p, _i, _p, _p, _i, _i, _i, _i, _i, _p, _p, _i, _f, _p, _i, _p, _p]
+            lib.dryft_gemm_stream.argtypes = [_p, _i, _p, _p, _i, _i, _i, _i, _i, _p, _p, _i, _f, _p, _i, _p, _p, _p, _p]
             lib.dryft_gemm_stream.restype = _i
             lib.dryft_gemm_stream_ss_parts.argtypes = [_i, _i]
             lib.dryft_gemm_stream_ss_parts.restype = _i
+            lib.dryft_gemm_stream_workspace_floats.restype = _ll
             _gemm_stream = lib
         return _gemm_stream
+
+
+_stream_scratch: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
+
+
+def gemm_stream_scratch(device: torch.device) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(workspace, tickets) of ``gemm_stream`` on this device: float32 slots for the pieces of tiles that two blocks
+    share, and zeroed int32 ticket counters (one per tile; every launch leaves them zero).  One set per device
+    serves every launch of a stream, because a launch only touches them after the launch before it has ended."""
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    sc = _stream_scratch.get(idx)
+    if sc is None:
+        dev = torch.device("cuda", idx)
+        with torch.cuda.device(dev):
+            n = int(gemm_stream_lib().dryft_gemm_stream_workspace_floats())
+        sc = (torch.empty(n, dtype=torch.float32, device=dev), torch.zeros(1 << 16, dtype=torch.int32, device=dev))
+        _stream_scratch[idx] = sc
+    return sc
 
 
 _gemm_tc: Optional[ctypes.CDLL] = None
@@ -608,6 +627,12 @@ def weighted_ahead_supported(k: int) -> bool:
     return k > 0 and k % 256 == 0
 
 
+def small_m_ss_parts(n: int, k: int) -> int:
+    """Blocks of sums of squares (64 floats each) that ``gemm_small_m(mode="residual")`` leaves for ``n`` outputs over
+    ``k`` inputs: one per 16-row tile."""
+    return (n + 15) // 16
+
+
 def gemm_small_m(a, w, out, *, mode: str = "store", norm_w=None, ss_in=None, ss_parts: int = 0, eps: float = 0.0,
                  ss_out=None, pdl: bool = False, xw_in=None, next_w=None, xw_out=None) -> None:
     """``a[M,K] @ w[.,K].T`` for up to 16 rows (decode; K a multiple of 16): bfloat16 operands, 32-bit accumulation,
@@ -615,8 +640,8 @@ def gemm_small_m(a, w, out, *, mode: str = "store", norm_w=None, ss_in=None, ss_
 
     * ``"store"``: ``out[M,N]`` (bfloat16 or float32) receives the product, ``w`` is ``[N,K]``;
     * ``"residual"``: ``out`` is the residual stream ``x[M,N]``, updated in place ``x += product``; with
-      ``ss_out`` ``[ceil(N/16), 64]`` float32 the per-row sums of squares of the new ``x`` are left there,
-      one partial per block of 16 columns;
+      ``ss_out`` ``[small_m_ss_parts(N, K), 64]`` float32 the per-row sums of squares of the new ``x`` are left
+      there, one partial per tile of up to 16 columns;
     * ``"silu"``: ``w`` is ``[2N,K]`` (gate rows, then up rows) and ``out[M,N] = silu(gate) * up``.
 
     With ``norm_w`` ``[K]`` float32 the rows of ``a`` are RMS-normalised on the fly; ``ss_in``
@@ -650,8 +675,8 @@ def gemm_small_m(a, w, out, *, mode: str = "store", norm_w=None, ss_in=None, ss_
         code = 2
         if ss_out is not None:
             _need(ss_out, "ss_out", torch.float32)
-            if ss_out.numel() < (n + 15) // 16 * SS_STRIDE:
-                raise KernelError("gemm_small_m: ss_out too small")
+            if ss_out.numel() < small_m_ss_parts(n, k) * SS_STRIDE:
+                raise KernelError("gemm_small_m: ss_out too small (small_m_ss_parts(N, K) blocks of 64 floats are left)")
     elif mode == "store":
         n = w.shape[0]
         _need(w, "w", torch.bfloat16, (n, k))
@@ -684,7 +709,8 @@ def gemm_small_m(a, w, out, *, mode: str = "store", norm_w=None, ss_in=None, ss_
                 _ok(rc, f"gemm_decode (M={m}, N={n}, K={k}, mode={mode}, activations weighted ahead; give norm_w for the other form)")
         rc = lib.dryft_gemm_decode(_ptr(a), k, _ptr(w), _ptr(out), n, code, m, n, _ptr(norm_w), _ptr(ss_in), int(ss_parts),
                                    float(eps), _ptr(ss_out), int(pdl), 0, _ptr(next_w), _ptr(xw_out), _stream())
-        if rc != UNSUPPORTED or xw_out is not None:  # the general form below cannot leave xw_out
+        if rc != UNSUPPORTED or xw_out is not None or ss_out is not None:
+            # the general form below cannot leave xw_out, and leaves another number of blocks of sums of squares
             _ok(rc, f"gemm_decode (M={m}, N={n}, K={k}, mode={mode})")
             return
     _ok(core().dryft_gemm_small_m(_ptr(a), k, _ptr(w), _ptr(out), n, code, m, n, k, _ptr(norm_w), _ptr(ss_in),
@@ -706,9 +732,9 @@ def gemm_stream_ss_parts(n_out: int, k_in: int) -> int:
 
 def gemm_stream(a, w, out, *, mode: str = "store", norm_w=None, ss_in=None, ss_parts: int = 0, eps: float = 0.0,
                 ss_out=None, pdl: bool = False) -> None:
-    """``gemm_small_m``'s contract for up to 64 rows, on tcgen05 with the weights streamed by TMA through
-    shared-memory rings and K split over a thread-block cluster.  ``ss_out`` must hold
-    ``gemm_stream_ss_parts(N, K)`` blocks of 64 floats."""
+    """``gemm_small_m``'s contract for up to 64 rows, on tcgen05 with the weights streamed by TMA through a
+    shared-memory ring, the work cut evenly over the SMs and tiles that two blocks share summed in block order.
+    ``ss_out`` must hold ``gemm_stream_ss_parts(N, K)`` blocks of 64 floats."""
     m, k = a.shape
     _need(a, "a", torch.bfloat16)
     if not gemm_stream_supported(m, k):
@@ -720,7 +746,11 @@ def gemm_stream(a, w, out, *, mode: str = "store", norm_w=None, ss_in=None, ss_p
     n = rows // 2 if mode == "silu" else rows
     _need(w, "w", torch.bfloat16, (2 * n if mode == "silu" else n, k))
     _need(out, "out", torch.float32 if code == 1 else torch.bfloat16, (m, n))
+    if n > (1 << 16) * 64:
+        raise KernelError(f"gemm_stream: {n} outputs are more than its ticket counters cover")
     if norm_w is not None:
+        if mode == "residual":
+            raise KernelError("gemm_stream: a residual product takes plain activations")
         _need(norm_w, "norm weight", torch.float32, (k,))
         _need(ss_in, "ss_in", torch.float32)
         if ss_parts <= 0 or ss_in.numel() < ss_parts * SS_STRIDE:
@@ -731,10 +761,40 @@ def gemm_stream(a, w, out, *, mode: str = "store", norm_w=None, ss_in=None, ss_p
         _need(ss_out, "ss_out", torch.float32)
         if ss_out.numel() < gemm_stream_ss_parts(n, k) * SS_STRIDE:
             raise KernelError("gemm_stream: ss_out too small")
+    ws, tk = gemm_stream_scratch(a.device)
     _ok(gemm_stream_lib().dryft_gemm_stream(_ptr(a), k, _ptr(w), _ptr(out), n, code, m, n, k, _ptr(norm_w), _ptr(ss_in),
                                             int(ss_parts), float(eps), _ptr(ss_out), int(pdl), _ptr(error_flag(a.device)),
-                                            _stream()),
+                                            _ptr(ws), _ptr(tk), _stream()),
         f"gemm_stream (M={m}, N={n}, K={k}, mode={mode})")
+
+
+def fused_rows_supported(m: int, k: int, small_m_max: int, stream_m_max: int) -> bool:
+    """Whether ``fused_product`` takes ``m`` rows over ``k`` inputs: the register-streaming product up to
+    ``small_m_max`` rows, the tcgen05 one up to ``stream_m_max``."""
+    if m <= min(small_m_max, SMALL_M_LIMIT):
+        return k % 16 == 0
+    return m <= min(stream_m_max, STREAM_M_LIMIT) and gemm_stream_supported(m, k)
+
+
+def fused_ss_parts(m: int, n: int, k: int, small_m_max: int) -> int:
+    """Blocks of sums of squares that ``fused_product(mode="residual")`` of these sizes leaves in ``ss_out``."""
+    if m <= min(small_m_max, SMALL_M_LIMIT):
+        return small_m_ss_parts(n, k)
+    return gemm_stream_ss_parts(n, k)
+
+
+def fused_product(a, w, out, *, small_m_max: int, **kw) -> None:
+    """A decode product with its norm / residual / SiLU*mul fused in, by the kernel that suits the row count:
+    ``gemm_small_m`` (weights streamed through registers into mma.sync) up to ``small_m_max`` rows, ``gemm_stream``
+    (TMA ring, tcgen05, even cut over the SMs) above.  Activations weighted ahead (``xw_in`` / ``xw_out``) belong
+    to the former only."""
+    if a.shape[0] <= min(small_m_max, SMALL_M_LIMIT):
+        gemm_small_m(a, w, out, **kw)
+        return
+    if kw.get("xw_in") is not None or kw.get("xw_out") is not None:
+        raise KernelError("fused_product: activations weighted ahead are not taken above small_m_max rows")
+    kw = {k_: v for k_, v in kw.items() if k_ not in ("xw_in", "xw_out", "next_w")}
+    gemm_stream(a, w, out, **kw)
 
 
 def row_sumsq(x, ss, norm_w=None, xw_out=None) -> None:

@@ -86,7 +86,7 @@ def decode_chain() -> None:
         if which == "gemm_stream":
             f, p1, p2 = K.gemm_stream, K.gemm_stream_ss_parts(hidden, q_dim), K.gemm_stream_ss_parts(hidden, inter)
         else:
-            f, p1, p2 = K.gemm_small_m, (hidden + 15) // 16, (hidden + 15) // 16
+            f, p1, p2 = K.gemm_small_m, K.small_m_ss_parts(hidden, q_dim), K.small_m_ss_parts(hidden, inter)
         ss0 = torch.zeros(64, device=DEV)
         K.row_sumsq(x, ss0)
         ss1, ss2 = torch.zeros(p1 * 64, device=DEV), torch.zeros(p2 * 64, device=DEV)

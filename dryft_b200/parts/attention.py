@@ -23,7 +23,7 @@ from ..cache.store import CacheEntry, KVNeed, StateNeed
 from ..config.spec import PartSpec
 from ..ops import kernels as K
 from .base import NORMS, POSITIONS, Runtime, StepContext, TensorInfo, fused_rms, register_mixer
-from .linear import linear, weighted_for
+from .linear import fusable_rows, linear, weighted_for
 
 PREFILL_TILE = 64      # query rows per block of the mma.sync prefill kernel
 PREFILL_TILE_TC = 128  # query rows per block of the tcgen05 prefill kernel
@@ -128,9 +128,8 @@ class Attention:
     def can_fuse(self, n_rows: int, norm) -> bool:
         """Few rows, bfloat16 everywhere, widths the weight-streaming product takes."""
         rt = self.rt
-        return (rt.fuse_decode and rt.is_bf16 and n_rows <= min(rt.small_m_max, K.SMALL_M_LIMIT)
-                and fused_rms(norm) is not None and self.w_qkv.dtype == torch.bfloat16
-                and self.w_o.dtype == torch.bfloat16 and self.hidden % 16 == 0 and self.q_dim % 16 == 0)
+        return (rt.fuse_decode and rt.is_bf16 and fusable_rows(n_rows, self.hidden, rt) and fusable_rows(n_rows, self.q_dim, rt)
+                and fused_rms(norm) is not None and self.w_qkv.dtype == torch.bfloat16 and self.w_o.dtype == torch.bfloat16)
 
     weighted_ahead = True   # forward_normed takes ``xw`` / ``next_norm`` and returns the weighted stream too
 
@@ -144,19 +143,21 @@ class Attention:
         w = self.w_qkv if owns_cache else self.w_qkv[: self.q_dim]
         qkv = torch.empty((n, w.shape[0]), dtype=x.dtype, device=x.device)
         norm_w, eps = fused_rms(norm)
+        small = self.rt.small_m_max
         if xw is not None and K.weighted_ahead_supported(self.hidden):
-            K.gemm_small_m(x, w, qkv, xw_in=xw, norm_w=norm_w, ss_in=ss, ss_parts=ss_parts, eps=eps, pdl=self.rt.pdl)
+            K.fused_product(x, w, qkv, small_m_max=small, xw_in=xw, norm_w=norm_w, ss_in=ss, ss_parts=ss_parts, eps=eps, pdl=self.rt.pdl)
         else:
-            K.gemm_small_m(x, w, qkv, norm_w=norm_w, ss_in=ss, ss_parts=ss_parts, eps=eps, pdl=self.rt.pdl)
+            K.fused_product(x, w, qkv, small_m_max=small, norm_w=norm_w, ss_in=ss, ss_parts=ss_parts, eps=eps, pdl=self.rt.pdl)
         o = self._attend(qkv, ctx, cache, owns_cache)
-        parts = (self.hidden + 15) // 16
+        parts = K.fused_ss_parts(n, self.hidden, self.q_dim, small)
         ss_out = torch.empty(parts * K.SS_STRIDE, dtype=torch.float32, device=x.device)
         xw_out = None
-        if weighted_for(next_norm, self.hidden, self.q_dim, self.rt):
+        if weighted_for(next_norm, self.hidden, self.q_dim, self.rt, n):
             xw_out = torch.empty_like(x)
-            K.gemm_small_m(o, self.w_o, x, mode="residual", ss_out=ss_out, pdl=self.rt.pdl, next_w=fused_rms(next_norm)[0], xw_out=xw_out)
+            K.fused_product(o, self.w_o, x, small_m_max=small, mode="residual", ss_out=ss_out, pdl=self.rt.pdl,
+                            next_w=fused_rms(next_norm)[0], xw_out=xw_out)
         else:
-            K.gemm_small_m(o, self.w_o, x, mode="residual", ss_out=ss_out, pdl=self.rt.pdl)
+            K.fused_product(o, self.w_o, x, small_m_max=small, mode="residual", ss_out=ss_out, pdl=self.rt.pdl)
         return ss_out, parts, xw_out
 
     def forward(self, h: torch.Tensor, ctx: StepContext, cache: CacheEntry, state, owns_cache: bool = True) -> torch.Tensor:

@@ -52,7 +52,7 @@ class PreNormBlock:
             ahead_f = getattr(self.ffn, "weighted_ahead", False)
             if ss is None:
                 ss = torch.empty(K.SS_STRIDE, dtype=torch.float32, device=x.device)
-                if ahead_m and weighted_for(self.norm_mixer, x.shape[1], x.shape[1], self.mixer.rt):
+                if ahead_m and weighted_for(self.norm_mixer, x.shape[1], x.shape[1], self.mixer.rt, x.shape[0]):
                     xw = torch.empty_like(x)
                     K.row_sumsq(x, ss, norm_w=fused_rms(self.norm_mixer)[0], xw_out=xw)
                 else:

@@ -13,7 +13,7 @@ import torch
 
 from ..ops import kernels as K
 from .base import Runtime, TensorInfo, fused_rms, register_embedding, register_head
-from .linear import linear
+from .linear import fusable_rows, linear
 
 
 @register_embedding("embedding")
@@ -71,17 +71,17 @@ class LMHead:
 
     def can_fuse(self, n_rows: int, norm) -> bool:
         rt = self.rt
-        return (rt.fuse_decode and rt.is_bf16 and n_rows <= min(rt.small_m_max, K.SMALL_M_LIMIT)
-                and fused_rms(norm) is not None and self.weight.dtype == torch.bfloat16
-                and self.weight.shape[1] % 16 == 0)
+        return (rt.fuse_decode and rt.is_bf16 and fusable_rows(n_rows, self.weight.shape[1], rt)
+                and fused_rms(norm) is not None and self.weight.dtype == torch.bfloat16)
 
     def forward_normed(self, x: torch.Tensor, ss, ss_parts: int, norm, xw=None) -> torch.Tensor:
         """Logits of every row of ``x`` with the final norm inside the product (decode); ``xw``: ``x``
         weighted by the final norm's weight already."""
         out = torch.empty((x.shape[0], self.vocab), dtype=torch.float32, device=x.device)
         norm_w, eps = fused_rms(norm)
+        small = self.rt.small_m_max
         if xw is not None and K.weighted_ahead_supported(x.shape[1]):
-            K.gemm_small_m(x, self.weight, out, xw_in=xw, norm_w=norm_w, ss_in=ss, ss_parts=ss_parts, eps=eps, pdl=self.rt.pdl)
+            K.fused_product(x, self.weight, out, small_m_max=small, xw_in=xw, norm_w=norm_w, ss_in=ss, ss_parts=ss_parts, eps=eps, pdl=self.rt.pdl)
         else:
-            K.gemm_small_m(x, self.weight, out, norm_w=norm_w, ss_in=ss, ss_parts=ss_parts, eps=eps, pdl=self.rt.pdl)
+            K.fused_product(x, self.weight, out, small_m_max=small, norm_w=norm_w, ss_in=ss, ss_parts=ss_parts, eps=eps, pdl=self.rt.pdl)
         return out

@@ -12,7 +12,7 @@ import torch
 
 from ..ops import kernels as K
 from .base import Runtime, StepContext, TensorInfo, fused_rms, register_ffn
-from .linear import linear, weighted_for
+from .linear import fusable_rows, linear, weighted_for
 
 
 @register_ffn("swiglu")
@@ -36,9 +36,8 @@ class SwiGLU:
 
     def can_fuse(self, n_rows: int, norm) -> bool:
         rt = self.rt
-        return (rt.fuse_decode and rt.is_bf16 and n_rows <= min(rt.small_m_max, K.SMALL_M_LIMIT)
-                and fused_rms(norm) is not None and self.w_gate_up.dtype == torch.bfloat16
-                and self.w_down.dtype == torch.bfloat16 and self.hidden % 16 == 0 and self.inter % 16 == 0)
+        return (rt.fuse_decode and rt.is_bf16 and fusable_rows(n_rows, self.hidden, rt) and fusable_rows(n_rows, self.inter, rt)
+                and fused_rms(norm) is not None and self.w_gate_up.dtype == torch.bfloat16 and self.w_down.dtype == torch.bfloat16)
 
     weighted_ahead = True   # forward_normed takes ``xw`` / ``next_norm`` and returns the weighted stream too
 
@@ -49,18 +48,22 @@ class SwiGLU:
         n = x.shape[0]
         act = torch.empty((n, self.inter), dtype=x.dtype, device=x.device)
         norm_w, eps = fused_rms(norm)
+        small = self.rt.small_m_max
         if xw is not None and K.weighted_ahead_supported(self.hidden):
-            K.gemm_small_m(x, self.w_gate_up, act, mode="silu", xw_in=xw, norm_w=norm_w, ss_in=ss, ss_parts=ss_parts, eps=eps, pdl=self.rt.pdl)
+            K.fused_product(x, self.w_gate_up, act, small_m_max=small, mode="silu", xw_in=xw, norm_w=norm_w, ss_in=ss, ss_parts=ss_parts,
+                            eps=eps, pdl=self.rt.pdl)
         else:
-            K.gemm_small_m(x, self.w_gate_up, act, mode="silu", norm_w=norm_w, ss_in=ss, ss_parts=ss_parts, eps=eps, pdl=self.rt.pdl)
-        parts = (self.hidden + 15) // 16
+            K.fused_product(x, self.w_gate_up, act, small_m_max=small, mode="silu", norm_w=norm_w, ss_in=ss, ss_parts=ss_parts, eps=eps,
+                            pdl=self.rt.pdl)
+        parts = K.fused_ss_parts(n, self.hidden, self.inter, small)
         ss_out = torch.empty(parts * K.SS_STRIDE, dtype=torch.float32, device=x.device)
         xw_out = None
-        if weighted_for(next_norm, self.hidden, self.inter, self.rt):
+        if weighted_for(next_norm, self.hidden, self.inter, self.rt, n):
             xw_out = torch.empty_like(x)
-            K.gemm_small_m(act, self.w_down, x, mode="residual", ss_out=ss_out, pdl=self.rt.pdl, next_w=fused_rms(next_norm)[0], xw_out=xw_out)
+            K.fused_product(act, self.w_down, x, small_m_max=small, mode="residual", ss_out=ss_out, pdl=self.rt.pdl,
+                            next_w=fused_rms(next_norm)[0], xw_out=xw_out)
         else:
-            K.gemm_small_m(act, self.w_down, x, mode="residual", ss_out=ss_out, pdl=self.rt.pdl)
+            K.fused_product(act, self.w_down, x, small_m_max=small, mode="residual", ss_out=ss_out, pdl=self.rt.pdl)
         return ss_out, parts, xw_out
 
     def _rows(self, h: torch.Tensor) -> torch.Tensor:

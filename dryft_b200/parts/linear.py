@@ -3,7 +3,8 @@
 
 Which product runs:
   * 32-bit activations (the 32-bit path): the hand-written CUDA-core product, true fp32;
-  * bfloat16, few rows (decode): the hand-written weight-streaming tensor-core product;
+  * bfloat16, few rows (decode): the hand-written weight-streaming tensor-core products -- through registers into
+    mma.sync up to ``small_m_max`` rows, by TMA into tcgen05.mma up to ``stream_m_max`` (64);
   * bfloat16, many rows (prefill): cuBLAS through ``torch.mm``, 32-bit accumulation — the library
     product the reference itself uses (``F.linear``, ``engine/dryft_qwen3/model.py:153,179,180``);
   * bfloat16 activations with a weight the checkpoint stores in 32-bit: the weight stays 32-bit,
@@ -44,15 +45,25 @@ def linear(x: torch.Tensor, w: torch.Tensor, rt: Runtime, out_dtype: Optional[to
         out = torch.empty((m, n), dtype=out_dtype, device=x.device)
         K.gemm_small_m(x, w, out)
         return out
+    if m <= min(rt.stream_m_max, K.STREAM_M_LIMIT) and K.gemm_stream_supported(m, k) and rt.tcgen05:
+        out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+        K.gemm_stream(x, w, out)
+        return out
     if out_dtype == torch.bfloat16:
         return torch.mm(x, w.t())
     return torch.mm(x, w.t(), out_dtype=out_dtype)
 
 
-def weighted_for(next_norm, width: int, k_in: int, rt: Runtime) -> bool:
+def fusable_rows(n_rows: int, k: int, rt: Runtime) -> bool:
+    """Whether the fused decode products take ``n_rows`` rows over ``k`` inputs."""
+    return K.fused_rows_supported(n_rows, k, rt.small_m_max, rt.stream_m_max if rt.tcgen05 else 0)
+
+
+def weighted_for(next_norm, width: int, k_in: int, rt: Runtime, n_rows: int = 1) -> bool:
     """Whether a fused decode product of ``k_in`` inputs that updates a stream of ``width`` should also leave
     the stream weighted for ``next_norm`` (an RMS norm over ``width``): both it and the product behind that
-    norm must be of the form compiled per inner size."""
+    norm must be of the form compiled per inner size (which takes up to ``small_m_max`` rows)."""
     rms = fused_rms(next_norm) if next_norm is not None else None
     return (rms is not None and rt.norm_ahead and rt.is_bf16 and rms[0].numel() == width
+            and n_rows <= min(rt.small_m_max, K.SMALL_M_LIMIT)
             and K.weighted_ahead_supported(width) and K.weighted_ahead_supported(k_in))

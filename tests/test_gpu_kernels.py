@@ -160,7 +160,7 @@ def test_gemm_small_m(m, n, k_, out_dtype):
 
 
 @pytest.mark.parametrize("m", [1, 8, 13])
-@pytest.mark.parametrize("n,k_", [(2560, 2560), (96, 176), (200, 1008), (4096, 1024), (208, 256)])
+@pytest.mark.parametrize("n,k_", [(2560, 2560), (96, 176), (200, 1008), (4096, 1024), (208, 256), (1000, 512)])
 def test_gemm_small_m_fused_norm_residual_silu(m, n, k_):
     """The fused forms of the decode product against the plain parts: RMSNorm of the input from
     sums of squares left by an earlier product, residual add with new sums of squares, SiLU*mul."""
@@ -182,7 +182,7 @@ def test_gemm_small_m_fused_norm_residual_silu(m, n, k_):
     # residual epilogue with sums of squares for the next norm
     res = torch.randn(m, n, device=DEV).to(bf)
     res0 = res.clone()
-    parts = (n + 15) // 16
+    parts = k.small_m_ss_parts(n, k_)
     ss_out = torch.full((parts * 64,), -1.0, device=DEV)
     k.gemm_small_m(x, w, res, mode="residual", ss_out=ss_out)
     prod = P.matmul_nt(x.cpu(), w.cpu(), bf)
@@ -229,10 +229,12 @@ def test_gemm_small_m_fused_norm_residual_silu(m, n, k_):
 @pytest.mark.parametrize("m", [1, 8, 13, 40, 64])
 @pytest.mark.parametrize("n,k_", [(2560, 2560), (6144, 2560), (2560, 9728), (1000, 192), (200, 128), (19456, 256)])
 def test_gemm_stream(m, n, k_):
-    """The weight-streaming decode product (tcgen05, TMA rings, cluster split-K) against the plain parts, in
-    every form: store (bfloat16 and 32-bit), norm prologue from sums of squares, residual add leaving new
-    sums of squares that a second product normalises from, SiLU*mul; 1..64 rows, output counts that are no
-    multiple of the 128-row tile, every cluster size."""
+    """The weight-streaming decode product (tcgen05, a TMA ring, the work cut evenly over the SMs, shared tiles
+    summed in block order through tickets) against the plain parts, in every form: store (bfloat16 and 32-bit),
+    norm on the way in from sums of squares, residual add leaving new sums of squares that a second product
+    normalises from, SiLU*mul with and without a norm; 1..64 rows; output counts that are no multiple of the
+    128-row tile; few tiles cut into many pieces (2,560 outputs over 9,728 inputs) and many tiles with few
+    pieces.  Launches repeat bit for bit and leave the ticket counters at zero."""
     k = K()
     bf = torch.bfloat16
     eps = 1e-5
@@ -273,13 +275,26 @@ def test_gemm_stream(m, n, k_):
         k.gemm_stream(res, w2, out2, norm_w=nw2, ss_in=ss_out, ss_parts=parts, eps=eps)
         ref2 = P.rmsnorm(res.cpu(), nw2.cpu(), eps).double() @ w2.cpu().double().T
         torch.testing.assert_close(out2.cpu().double(), ref2, rtol=2e-2, atol=2e-2)
-    # SiLU*mul over gate rows then up rows
+    # SiLU*mul over gate rows then up rows, plain and with the norm on the way in
     inter = n // 2
     act = torch.empty(m, inter, device=DEV, dtype=bf)
     k.gemm_stream(x, w[: 2 * inter], act, mode="silu")
     gu = P.matmul_nt(x.cpu(), w[: 2 * inter].cpu(), bf)
     torch.testing.assert_close(act.cpu().float(), P.silu_mul(gu[:, :inter], gu[:, inter:]).float(), rtol=3e-2, atol=3e-2)
+    act_n = torch.empty(m, inter, device=DEV, dtype=bf)
+    k.gemm_stream(x, w[: 2 * inter], act_n, mode="silu", norm_w=nw, ss_in=ss, ss_parts=1, eps=eps)
+    gu = P.matmul_nt(h_ref, w[: 2 * inter].cpu(), bf)
+    torch.testing.assert_close(act_n.cpu().float(), P.silu_mul(gu[:, :inter], gu[:, inter:]).float(), rtol=3e-2, atol=3e-2)
+    # the same launches again: the same bits (pieces are added in block order, whoever finishes last), tickets at zero
+    again = torch.empty_like(out32)
+    k.gemm_stream(x, w, again)
+    assert torch.equal(again, out32)
+    res2 = res0.clone()
+    ss2 = torch.full((parts * 64,), -1.0, device=DEV)
+    k.gemm_stream(x, w, res2, mode="residual", ss_out=ss2)
+    assert torch.equal(res2, res) and torch.equal(ss2.view(parts, 64)[:, :m], ss_out.view(parts, 64)[:, :m])
     torch.cuda.synchronize()
+    assert int(k.gemm_stream_scratch(torch.device(DEV, 0))[1].abs().sum()) == 0
     k.check_error_flags()
 
 
