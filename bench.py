@@ -342,7 +342,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (named in config)")
     ap.add_argument("--preset", default="qwen3-4b")
     ap.add_argument("--no-points", action="store_true")
-    ap.add_argument("--phase", default="all", choices=["all", "decode", "prefill", "timeline"],
+    ap.add_argument("--phase", default="all", choices=["all", "decode", "prefill"],
                     help="time only one phase (for profiling); the JSON line then carries only that phase")
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--small-m-max", type=int, default=None,
@@ -385,13 +385,6 @@ def main() -> int:
     if args.phase == "prefill":
         pf_ms = prefill_time(eng, 2048, 3, args.seed + 2)
         print(json.dumps({"phase": "prefill", "tokens": 2048, "ms": pf_ms, "tok_s": 2048 / (pf_ms * 1e-3)}))
-        return 0
-    if args.phase == "timeline":
-        # block timeline of the last decode steps (microseconds from the first block shown); needs DRYFT_B200_TRACE=1
-        from dryft_b200.ops import timeline
-        decode_device_time(eng, args.batch, args.prompt_len, 8, warmup, args.seed)
-        torch.cuda.synchronize()
-        print(timeline.launch_table(timeline.collect(), last_us=400.0, max_launches=12))
         return 0
     if args.phase == "decode":
         ms, launches, mean_ctx = decode_device_time(eng, args.batch, args.prompt_len, args.steps, warmup, args.seed)

@@ -198,8 +198,6 @@ __global__ void __launch_bounds__(NWARP * 32) attn_decode_kernel(const Params p)
   const int nH = p.nKV * G;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int g = lane >> 2, t = lane & 3;
-
-  DRYFT_TRACE_NOW(tr0);
   pdl_launch_dependents();
   // What does not depend on the projection before this launch is done before waiting for it: the step's
   // token metadata and page table (complete before the step's first programmatic launch; the block's
@@ -261,8 +259,6 @@ __global__ void __launch_bounds__(NWARP * 32) attn_decode_kernel(const Params p)
   }
 
   pdl_wait();  // the projection that made qkv is complete
-
-  DRYFT_TRACE_NOW(tr1);
   if (slot < 0) {  // padding row: defined zeros (written by split 0), no cache access, no ticket
     if (split == 0)
       for (int i = tid; i < G * D; i += THREADS) p.out[(size_t)n * nH * D + (size_t)kvh * G * D + i] = __float2bfloat16_rn(0.f);
@@ -300,7 +296,6 @@ __global__ void __launch_bounds__(NWARP * 32) attn_decode_kernel(const Params p)
     }
   }
   __syncthreads();  // queries (and the new key and value) are in shared memory
-  DRYFT_TRACE_NOW(tr2);
 
   // ---- each warp walks its own 16-key slices of the block's pages ----
   float o_acc[DT][4];
@@ -466,10 +461,7 @@ __global__ void __launch_bounds__(NWARP * 32) attn_decode_kernel(const Params p)
       if (d == 0) { p.part_ml[(pidx * G + h) * 2] = mx; p.part_ml[(pidx * G + h) * 2 + 1] = den; }
     }
   }
-  if (p.n_splits == 1) {
-    DRYFT_TRACE_PUT(1u, tr0, tr1, tr2);
-    return;
-  }
+  if (p.n_splits == 1) return;
   if (p.cluster) {
     // ---- the splits are the blocks of one cluster: every block combines a slice of the outputs over
     // all blocks' partials, in split order, reading them through distributed shared memory ----
@@ -490,7 +482,6 @@ __global__ void __launch_bounds__(NWARP * 32) attn_decode_kernel(const Params p)
       p.out[((size_t)n * nH + kvh * G + h) * D + d] = __float2bfloat16_rn(den > 0.f ? num / den : 0.f);
     }
     cluster_sync_all();   // nobody leaves while another block may still read its partial
-    DRYFT_TRACE_PUT(1u, tr0, tr1, tr2);
     return;
   }
 
@@ -578,7 +569,6 @@ static int launch_shape(const Params& p, int n_rows, int nKV, int n_splits, int 
 
 DRYFT_API int dryft_attn_decode_head_dim() { return D; }
 DRYFT_API int dryft_attn_decode_group() { return G; }
-DRYFT_TRACE_EXPORT(dryft_attn_decode_trace)
 
 DRYFT_API int dryft_attn_decode(const void* qkv, int qkv_stride, const float* wq, const float* wk, const float* inv_freq,
                                 const int* tok_slot, const int* tok_pos, void* k_pages, void* v_pages,

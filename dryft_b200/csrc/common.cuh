@@ -67,41 +67,3 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 }
 
 static inline int launch_status() { return (int)cudaGetLastError(); }
-
-// ------------------------------------------------------------------------------------------
-// Block timeline (development aid, compiled in only with -DDRYFT_TRACE): thread 0 of a block notes
-// the device-wide nanosecond clock at a few points of its life; the records of all blocks of all
-// launches of a library land in a ring in device memory that DRYFT_TRACE_EXPORT's function copies to
-// the host.  It shows how consecutive launches overlap on the SMs.
-// ------------------------------------------------------------------------------------------
-#ifdef DRYFT_TRACE
-struct DryftTraceRec { unsigned long long t[4]; unsigned tag, block, sm, n_blocks; };
-constexpr unsigned DRYFT_TRACE_CAP = 1u << 17;
-static __device__ DryftTraceRec dryft_trace_buf[DRYFT_TRACE_CAP];
-static __device__ unsigned dryft_trace_count;
-__device__ __forceinline__ unsigned long long dryft_now() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ void dryft_trace_put(unsigned tag, unsigned long long t0, unsigned long long t1, unsigned long long t2) {
-  unsigned sm;
-  asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
-  DryftTraceRec& r = dryft_trace_buf[atomicAdd(&dryft_trace_count, 1u) % DRYFT_TRACE_CAP];
-  r.t[0] = t0; r.t[1] = t1; r.t[2] = t2; r.t[3] = dryft_now();
-  r.tag = tag; r.block = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z); r.sm = sm;
-  r.n_blocks = gridDim.x * gridDim.y * gridDim.z;
-}
-#define DRYFT_TRACE_EXPORT(name)                                                                          \
-  DRYFT_API int name(void* host, unsigned* count) {                                                       \
-    cudaError_t e = cudaMemcpyFromSymbol(count, dryft_trace_count, sizeof(unsigned));                     \
-    if (e != cudaSuccess) return (int)e;                                                                  \
-    return (int)cudaMemcpyFromSymbol(host, dryft_trace_buf, sizeof(DryftTraceRec) * DRYFT_TRACE_CAP);     \
-  }
-#define DRYFT_TRACE_NOW(var) const unsigned long long var = threadIdx.x == 0 ? dryft_now() : 0ull
-#define DRYFT_TRACE_PUT(tag, t0, t1, t2) do { if (threadIdx.x == 0) dryft_trace_put(tag, t0, t1, t2); } while (0)
-#else
-#define DRYFT_TRACE_EXPORT(name)
-#define DRYFT_TRACE_NOW(var)
-#define DRYFT_TRACE_PUT(tag, t0, t1, t2)
-#endif

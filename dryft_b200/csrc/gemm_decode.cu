@@ -87,8 +87,6 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
   constexpr int TILE_N = MODE == SILU ? 8 : ROWS;
   const int n_tiles = (N + TILE_N - 1) / TILE_N;
   const int k_warp = warp * SPW * 32 + t * 8;   // this thread's first k
-
-  DRYFT_TRACE_NOW(tr0);
   pdl_launch_dependents();
 
   uint4 wa[CHUNK], wb[CHUNK];
@@ -130,7 +128,6 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
   }
 
   pdl_wait();  // from here on, what earlier launches wrote (activations, sums of squares) is visible
-  DRYFT_TRACE_NOW(tr1);
 
   // SCALED: the rows' sums of squares are requested now and added after the first tile's products, so
   // that nothing waits for them: warp w owns rows w, w + 8, ...; a lane holds up to SSL blocks per row
@@ -235,8 +232,6 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
   constexpr bool STAGED = PRO != PLAIN;   // the block's activations are in shared memory
   const bf16* a_frag = STAGED ? a_res + (size_t)g * KA + k_warp : A + (size_t)g * lda + k_warp;
   const size_t a_mb = STAGED ? (size_t)8 * KA : (size_t)8 * lda;
-
-  DRYFT_TRACE_NOW(tr2);
   int buf = 0;
   for (; tile < n_tiles; tile += gridDim.x) {
     float acc[MB][4];
@@ -338,7 +333,6 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
       }
     }
   }
-  DRYFT_TRACE_PUT((unsigned)(K * 16 + MODE * 2 + (PRO != PLAIN ? 1 : 0)), tr0, tr1, tr2);
 }
 
 template <int MB, int MODE, int PRO>
@@ -411,7 +405,6 @@ int launch1(int mode, int pro, const Args& a) {
 }  // namespace
 
 DRYFT_API int dryft_gemm_decode_k() { return K; }
-DRYFT_TRACE_EXPORT(dryft_gemm_decode_trace)
 
 // Same contract as dryft_gemm_small_m (csrc/gemm_small_m.cu) for this library's K.  A residual product
 // of N outputs leaves ceil(N/16) blocks of sums of squares in ss_out and, given the next norm's weight

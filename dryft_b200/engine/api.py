@@ -50,7 +50,11 @@ class EngineOptions:
                                            # which is faster today: profiles/gemm_stream_microbench.md)
     fuse_decode: bool = True               # fold norms, adds and SiLU*mul into the decode products
     pdl: bool = True                       # programmatic dependent launch between the decode products
-    norm_ahead: bool = True                # fused decode: the next norm's weight is applied by the product before it
+    # fused decode: the next norm's weight is applied by the product before it and the norm's factor by the product
+    # behind it.  3 % faster at batch 1 to 8, but the activations are then rounded once where the reference rounds twice
+    # (engine/dryft_qwen3/model.py:28-32): as close to 32-bit as the default, 1.3 times further from a plain bfloat16
+    # evaluation.  Off by default: the default path keeps the reference's rounding points.
+    norm_ahead: bool = False
     tcgen05: bool = True                   # prefill attention on tcgen05 / TMEM / TMA where the head size allows
     # Prompts longer than this go through the step function in chunks of this many tokens per sequence (the same
     # step again, from the cache the chunk before left): bounds the step's activations ([tokens, q + 2 kv], the

@@ -95,11 +95,8 @@ def library_path(name: str, sources: Sequence[str], defines: Optional[Dict[str, 
 
 def build_library(name: str, sources: Sequence[str], defines: Optional[Dict[str, int]] = None,
                   extra_flags: Iterable[str] = ()) -> str:
-    """Path of the shared library, compiling it first if it is not there yet.  With DRYFT_B200_TRACE=1 in
-    the environment the kernels that carry block-timeline points are built with them (a different file)."""
+    """Path of the shared library, compiling it first if it is not there yet."""
     defines = dict(defines or {})
-    if os.environ.get("DRYFT_B200_TRACE") == "1":
-        defines["DRYFT_TRACE"] = 1
     out = library_path(name, sources, defines)
     if os.path.isfile(out):
         return out

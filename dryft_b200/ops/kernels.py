@@ -148,39 +148,6 @@ def gemm_stream_scratch(device: torch.device) -> Tuple[torch.Tensor, torch.Tenso
     return sc
 
 
-_gemm_tc: Optional[ctypes.CDLL] = None
-
-
-def gemm_tc_lib() -> ctypes.CDLL:
-    """The tcgen05 / TMEM / TMA matrix product of the prefill path."""
-    global _gemm_tc
-    with _lock:
-        if _gemm_tc is None:
-            lib = _load(build.build_library("gemm_tc", ("gemm_tc.cu",)))
-            lib.dryft_gemm_tc.argtypes = [_p, _p, _p, _i, _i, _i, _i, _i, _p, _p]
-            lib.dryft_gemm_tc.restype = _i
-            _gemm_tc = lib
-        return _gemm_tc
-
-
-def gemm_tc(a, w, out, *, mode: str = "store") -> None:
-    """``a[M,K] @ w[.,K].T`` on the 5th-generation tensor cores (bfloat16, K a multiple of 64), many rows
-    (prefill).  ``mode``: ``"store"`` writes ``out[M,N]``; ``"residual"`` adds the product into the stream
-    ``out[M,N]`` in place; ``"silu"`` takes ``w`` ``[2N,K]`` (gate rows, then up rows) and writes
-    ``silu(gate) * up``.  A bounded wait that runs out inside the kernel raises the device error flag
-    (``check_error_flags``)."""
-    m, k = a.shape
-    _need(a, "a", torch.bfloat16)
-    code = {"store": 0, "residual": 2, "silu": 3}.get(mode)
-    if code is None:
-        raise KernelError(f"gemm_tc: unknown mode {mode!r}")
-    n = w.shape[0] // 2 if mode == "silu" else w.shape[0]
-    _need(w, "w", torch.bfloat16, ((2 * n if mode == "silu" else n), k))
-    _need(out, "out", torch.bfloat16, (m, n))
-    _ok(gemm_tc_lib().dryft_gemm_tc(_ptr(a), _ptr(w), _ptr(out), n, code, m, n, k, _ptr(error_flag(a.device)), _stream()),
-        f"gemm_tc (M={m}, N={n}, K={k}, mode={mode})")
-
-
 def attention_decode_supported(head_dim: int, group: int) -> bool:
     """Whether the one-launch decode attention exists for these sizes (the query heads of a kv head
     form one 16-row tensor-core operand)."""

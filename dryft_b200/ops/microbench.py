@@ -1,9 +1,12 @@
 """Kernel microbenchmarks on Qwen3-4B shapes: ``python -m dryft_b200.ops.microbench <what>``.
 
 ``attn-prefill``   causal prompt attention of one sequence: mma.sync kernel against the tcgen05 kernel
-``gemm-tc``        the tcgen05 prefill product against the library product (torch.mm)
 ``decode-chain``   a layer's four decode products as a chain of programmatic launches in a CUDA graph,
                    36 layers with weights of their own: gemm_small_m / gemm_decode against gemm_stream
+``decode-products``  each of a layer's four products alone (36 weights of its own, in a CUDA graph), 8 / 16 / 64 rows:
+                   gemm_small_m, gemm_stream (with its fusions, and as a plain store) and the library's torch.mm
+
+The functions take the sizes as arguments (``layers``, ``rows``, ``tokens``) so that a test can run them small.
 
 Timed with CUDA events after warm-ups; inputs of a chain are larger than L2.  The numbers quoted under
 ``profiles/`` come from here.  hari495/dryft times whole generations only (``agent/bench.py``).
@@ -34,9 +37,9 @@ def _time(fn, iters: int) -> float:
     return s.elapsed_time(e) * 1000.0 / iters   # microseconds
 
 
-def attn_prefill() -> None:
+def attn_prefill(token_counts=(2048, 8192)) -> None:
     n_heads, n_kv, d, page = 32, 8, 128, 64
-    for tokens in (2048, 8192):
+    for tokens in token_counts:
         n_pages = (tokens + page - 1) // page + 1
         kc = torch.randn(n_pages, n_kv, page, d, device=DEV).to(BF)
         vc = torch.randn_like(kc)
@@ -55,22 +58,8 @@ def attn_prefill() -> None:
     K.check_error_flags()
 
 
-def gemm_tc() -> None:
-    for m, n, k, mode in ((2048, 6144, 2560, "store"), (2048, 2560, 4096, "residual"), (2048, 9728, 2560, "silu"),
-                          (2048, 2560, 9728, "residual"), (8192, 9728, 2560, "silu")):
-        a = torch.randn(m, k, device=DEV).to(BF)
-        w = (torch.randn(2 * n if mode == "silu" else n, k, device=DEV) * 0.02).to(BF)
-        out = torch.zeros(m, n, device=DEV, dtype=BF)
-        flops = 2.0 * m * w.shape[0] * k
-        us = _time(lambda: K.gemm_tc(a, w, out, mode=mode), 10)
-        ref = _time(lambda: torch.mm(a, w.t()), 10)
-        print(f"{m} x {n} x {k} {mode:8s}: gemm_tc {us:7.1f} us {flops / us / 1e6:5.0f} TFLOP/s | torch.mm (product only) "
-              f"{ref:7.1f} us {flops / ref / 1e6:5.0f} TFLOP/s", flush=True)
-    K.check_error_flags()
-
-
-def decode_chain() -> None:
-    hidden, q_dim, inter, layers = 2560, 4096, 9728, 36
+def decode_chain(layers: int = 36, small_rows=(1, 8), stream_rows=(16, 32, 64)) -> None:
+    hidden, q_dim, inter = 2560, 4096, 9728
     w_qkv = (torch.randn(layers, 6144, hidden, device=DEV) * 0.02).to(BF)
     w_o = (torch.randn(layers, hidden, q_dim, device=DEV) * 0.02).to(BF)
     w_gu = (torch.randn(layers, 2 * inter, hidden, device=DEV) * 0.02).to(BF)
@@ -108,16 +97,59 @@ def decode_chain() -> None:
         us = _time(g.replay, 5) / layers
         print(f"{which:12s} M={m:2d}: {us:7.2f} us/layer  {weight_bytes / us / 1e6:5.2f} TB/s", flush=True)
 
-    for m in (1, 8):
+    for m in small_rows:
         run("gemm_small_m", m)
         run("gemm_stream", m)
-    for m in (16, 32, 64):
+    for m in stream_rows:
         run("gemm_stream", m)
     K.check_error_flags()
 
 
+def decode_products(layers: int = 36, rows=(8, 16, 64)) -> None:
+    """Microseconds per product, each product alone (its ``layers`` weights one after the other in a CUDA graph)."""
+    shapes = {"qkv": (6144, 2560, "store", True), "o_proj": (2560, 4096, "residual", False),
+              "gate|up": (9728, 2560, "silu", True), "down": (2560, 9728, "residual", False)}
+
+    def graph_us(fn) -> float:
+        fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        return _time(g.replay, 5) / layers
+
+    for m in rows:
+        for name, (n, k, mode, norm) in shapes.items():
+            n_rows = 2 * n if mode == "silu" else n
+            ws = [(torch.randn(n_rows, k, device=DEV) * 0.02).to(BF) for _ in range(layers)]
+            x = torch.randn(m, k, device=DEV).to(BF)
+            nw = torch.ones(k, device=DEV)
+            ss = torch.zeros(64, device=DEV)
+            K.row_sumsq(x, ss)
+            out = torch.zeros(m, n, device=DEV, dtype=BF)
+            ss_stream = torch.zeros(K.gemm_stream_ss_parts(n, k) * 64, device=DEV)
+            ss_small = torch.zeros(K.small_m_ss_parts(n, k) * 64, device=DEV)
+
+            def fused(f, ss_out):
+                for w in ws:
+                    if norm:
+                        f(x, w, out, mode=mode, norm_w=nw, ss_in=ss, ss_parts=1, eps=1e-6, pdl=True)
+                    else:
+                        f(x, w, out, mode=mode, ss_out=ss_out, pdl=True)
+
+            res = {"gemm_stream": graph_us(lambda: fused(K.gemm_stream, ss_stream)),
+                   "gemm_stream, plain store": graph_us(lambda: [K.gemm_stream(x, w[:n], out, pdl=True) for w in ws]),
+                   "torch.mm": graph_us(lambda: [torch.mm(x, w.t()) for w in ws])}
+            if m <= K.SMALL_M_LIMIT:
+                res["gemm_small_m"] = graph_us(lambda: fused(K.gemm_small_m, ss_small))
+            mb = n_rows * k * 2 / 1e6
+            print(f"M={m:3d} {name:8s} {mb:6.1f} MB | " + " | ".join(f"{a} {b:6.1f} us" for a, b in res.items()), flush=True)
+            del ws
+    K.check_error_flags()
+
+
 def main(argv) -> int:
-    what = {"attn-prefill": attn_prefill, "gemm-tc": gemm_tc, "decode-chain": decode_chain}
+    what = {"attn-prefill": attn_prefill, "decode-chain": decode_chain, "decode-products": decode_products}
     if len(argv) != 2 or argv[1] not in what:
         print("usage: python -m dryft_b200.ops.microbench " + "|".join(what), file=sys.stderr)
         return 2

@@ -56,7 +56,7 @@ class Runtime:
     ffn_chunk_rows: int = 16384  # rows of the feed-forward processed at once (bounds [rows, 2I])
     fuse_decode: bool = True     # few rows: fold norms, residual adds and SiLU*mul into the products
     pdl: bool = True             # launch the fused decode products as programmatic dependents
-    norm_ahead: bool = True      # fused decode: a residual product leaves the stream weighted for the next norm
+    norm_ahead: bool = False     # fused decode: a residual product leaves the stream weighted for the next norm (one rounding fewer than the reference)
     tcgen05: bool = True         # prompts: attention on tcgen05.mma / tensor memory / TMA where sizes allow
 
     @property

@@ -298,40 +298,6 @@ def test_gemm_stream(m, n, k_):
     k.check_error_flags()
 
 
-@pytest.mark.parametrize("m,n,k_", [(128, 256, 64), (100, 300, 128), (333, 2560, 512), (2048, 1024, 2560)])
-@pytest.mark.parametrize("mode", ["store", "residual", "silu"])
-def test_gemm_tc(m, n, k_, mode):
-    """The tcgen05 / TMEM / TMA product (prefill) against a 64-bit reference: plain store, residual add
-    in place, SiLU*mul over gate rows then up rows; row and column counts that are no multiple of the
-    128 x 256 tile."""
-    k = K()
-    bf = torch.bfloat16
-    a = torch.randn(m, k_, device=DEV).to(bf)
-    rows = 2 * n if mode == "silu" else n
-    w = (torch.randn(rows, k_, device=DEV) / math.sqrt(k_)).to(bf)
-    out = torch.randn(m, n, device=DEV).to(bf)
-    x0 = out.clone()
-    k.gemm_tc(a, w, out, mode=mode)
-    torch.cuda.synchronize()
-    k.check_error_flags()
-    prod = P.matmul_nt(a.cpu(), w.cpu(), bf)
-    if mode == "store":
-        want = prod
-    elif mode == "residual":
-        want = P.residual_add(x0.cpu(), prod)
-    else:
-        want = P.silu_mul(prod[:, :n], prod[:, n:])
-    torch.testing.assert_close(out.cpu().float(), want.float(), rtol=2e-2, atol=3e-2)
-
-
-def test_gemm_tc_refuses_what_it_cannot_take():
-    k = K()
-    a = torch.zeros(128, 96, device=DEV, dtype=torch.bfloat16)  # K is no multiple of 64
-    w = torch.zeros(64, 96, device=DEV, dtype=torch.bfloat16)
-    with pytest.raises(k.KernelError):
-        k.gemm_tc(a, w, torch.empty(128, 64, device=DEV, dtype=torch.bfloat16))
-
-
 def test_gemm_small_m_refuses_odd_k():
     k = K()
     a = torch.zeros(2, 12, device=DEV, dtype=torch.bfloat16)
@@ -763,3 +729,23 @@ def test_sample_rows_matches_plain(vocab, temperature, top_k):
         got = out.tolist()
         want = [P.choose_token(lg[r], temperature, top_k, P.uniform_draw(1234, int(seqs[r]), step)) for r in range(rows)]
         assert got == want, (step, got, want)
+
+
+# ------------------------------------------------------------------------------------ the timing tool
+def test_microbench_runs_small(capsys):
+    """``python -m dryft_b200.ops.microbench``'s functions at sizes a test can afford: every line they print carries
+    a positive time (the numbers under ``profiles/`` come from the same functions at full size)."""
+    from dryft_b200.ops import microbench
+
+    with torch.no_grad():
+        microbench.attn_prefill(token_counts=(256,))
+        microbench.decode_chain(layers=1, small_rows=(8,), stream_rows=(16,))
+        microbench.decode_products(layers=1, rows=(8, 64))
+    lines = [ln for ln in capsys.readouterr().out.splitlines() if ln.strip()]
+    assert len(lines) == 2 + 3 + 8
+    import re
+
+    for ln in lines:
+        times = [float(t) for t in re.findall(r"([0-9.]+) us", ln)]
+        assert times and all(t > 0 for t in times), ln
+    assert microbench.main(["microbench", "no-such-thing"]) == 2

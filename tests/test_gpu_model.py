@@ -286,29 +286,42 @@ def test_fused_decode_products_equal_the_separate_kernels(model_dirs):
 
 
 def test_norm_split_over_two_launches(model_dirs):
-    """At widths that are multiples of 256 a fused decode product leaves the stream weighted for the next
-    norm and the product behind that norm scales its sums instead of normalising its input.  Decoding token
-    by token must stay within bfloat16 rounding of the plain implementation and of the same engine with the
-    split switched off; CUDA-graph decoding must give the same tokens as eager decoding."""
-    on = engine_for(model_dirs, "d", torch.bfloat16)
-    off = engine_for(model_dirs, "d", torch.bfloat16, norm_ahead=False)
-    toks = H.prompts_for("d", [60], seed=21)[0]
-    outs = []
-    for eng in (on, off):
-        s = eng.cache.open_sequences(1)
-        rows = [step(eng, s, [toks[:28]], [[27]])]
-        for t in toks[28:]:
-            rows.append(step(eng, s, [[t]], [[0]]))
-        eng.cache.close_sequences(s)
-        outs.append(torch.cat(rows).float().cpu())
-    p32 = plain_for(model_dirs, "d", torch.float32).logits(toks)[27:]
-    pb = plain_for(model_dirs, "d", torch.bfloat16).logits(toks)[27:]
-    tol = H.bf16_tol(pb, p32)
-    assert not torch.equal(outs[0], outs[1]), "the split path did not run"
-    assert H.rel_err(outs[0], pb) <= tol and H.rel_err(outs[1], pb) <= tol
-    assert H.rel_err(outs[0], outs[1]) <= tol
+    """An option (``norm_ahead=True``; off by default): at widths that are multiples of 256 a fused decode product
+    leaves the stream weighted for the next norm and the product behind that norm scales its sums instead of
+    normalising its input -- the activations are then rounded once where the reference rounds twice
+    (``engine/dryft_qwen3/model.py:28-32``).  Measured on this configuration and at the Qwen3-4B widths (2 and 8
+    layers): the option's logits are as close to the plain 32-bit ones as the default's (0.98 to 1.09 times its
+    error) and up to 1.36 times as far from the plain bfloat16 ones.  Asserted here: the option runs (other bits),
+    stays within those factors, and the default stays within bfloat16 rounding of the plain implementation;
+    CUDA-graph decoding gives the same tokens as eager decoding with the option on."""
+    on = engine_for(model_dirs, "d", torch.bfloat16, norm_ahead=True)
+    off = engine_for(model_dirs, "d", torch.bfloat16)
+    assert off.rt.norm_ahead is False, "the default path keeps the reference's rounding points"
+    errs = {"on": [], "off": []}
+    differs = False
+    p32m, pbm = plain_for(model_dirs, "d", torch.float32), plain_for(model_dirs, "d", torch.bfloat16)
+    for seed in (21, 22, 23):
+        toks = H.prompts_for("d", [60], seed=seed)[0]
+        p32, pb = p32m.logits(toks)[27:], pbm.logits(toks)[27:]
+        tol = H.bf16_tol(pb, p32)
+        outs = {}
+        for name, eng in (("on", on), ("off", off)):
+            s = eng.cache.open_sequences(1)
+            rows = [step(eng, s, [toks[:28]], [[27]])]
+            for t in toks[28:]:
+                rows.append(step(eng, s, [[t]], [[0]]))
+            eng.cache.close_sequences(s)
+            outs[name] = torch.cat(rows).float().cpu()
+            errs[name].append((H.rel_err(outs[name], pb), H.rel_err(outs[name], p32)))
+            assert H.rel_err(outs[name], pb) <= tol
+        differs = differs or not torch.equal(outs["on"], outs["off"])
+    assert differs, "the split path did not run"
+    on_b, off_b = max(e[0] for e in errs["on"]), max(e[0] for e in errs["off"])
+    on_32, off_32 = max(e[1] for e in errs["on"]), max(e[1] for e in errs["off"])
+    assert on_32 <= 1.25 * off_32, f"the option is further from 32-bit than measured: {on_32:.4f} vs {off_32:.4f}"
+    assert on_b <= 1.6 * off_b, f"the option is further from plain bfloat16 than measured: {on_b:.4f} vs {off_b:.4f}"
     prompts = H.prompts_for("d", [9, 2, 40], seed=8)
-    eager = engine_for(model_dirs, "d", torch.bfloat16, cuda_graphs=False)
+    eager = engine_for(model_dirs, "d", torch.bfloat16, cuda_graphs=False, norm_ahead=True)
     assert [s for s in on.generate(prompts, 16)] == [s for s in eager.generate(prompts, 16)]
     from dryft_b200.ops import kernels as K
     K.check_error_flags()

@@ -140,12 +140,14 @@ def test_wide_whole_and_last_32_one_by_one(dirs, dtype):
     eng.cache.check()
 
 
-@pytest.mark.parametrize("dtype", DTYPES)
-def test_wide_unequal_batches_of_12_16_64(dirs, dtype):
+@pytest.mark.parametrize("dtype,stream", [(torch.float32, 0), (torch.bfloat16, 0), (torch.bfloat16, 64)])
+def test_wide_unequal_batches_of_12_16_64(dirs, dtype, stream):
     """Above eight rows the decode step changes kernels (library products, separate norm and SiLU*mul launches,
-    narrower attention blocks); as sequences end the batch shrinks through 8 rows into the fused products.
-    Three batches in a row on the same slots."""
-    eng = engine(dirs, "wide", dtype, max_batch=64, max_seq_len=1280, max_tokens=64 * 128 + 2048)
+    narrower attention blocks; or, with ``stream_m_max=64``, the tcgen05 weight-streaming products with the norm,
+    the residual add and SiLU*mul fused in); as sequences end the batch shrinks through 8 rows into the
+    register-streaming products.  Three batches in a row on the same slots."""
+    kw = dict(stream_m_max=stream) if stream else {}
+    eng = engine(dirs, "wide", dtype, max_batch=64, max_seq_len=1280, max_tokens=64 * 128 + 2048, **kw)
     g = torch.Generator().manual_seed(77)
     seed = 100
     for n_seqs in (12, 16, 64):
@@ -203,6 +205,20 @@ def test_wide_generation_across_the_1024_context_edge(dirs, dtype):
     from dryft_b200.ops import kernels as K
     K.check_error_flags()
     assert eng.cache.slots.n_held == 0
+
+
+def test_wide_generation_with_the_streaming_products_equals_their_step_by_step_run(dirs):
+    """``stream_m_max=64``: seventeen sequences decoded through the captured graph (programmatic launches, tickets
+    and workspace shared by all layers) must give the tokens of the plain model, twice over."""
+    eng = engine(dirs, "wide", torch.bfloat16, max_batch=64, max_seq_len=1280, max_tokens=64 * 128 + 2048, stream_m_max=64)
+    ps = prompts("wide", [3, 17, 8, 30, 1, 12, 25, 6, 9, 14, 2, 21, 5, 11, 7, 19, 4], 43)
+    out = [s for s in eng.generate(ps, 10)]
+    assert [s for s in eng.generate(ps, 10)] == out
+    for b, p in enumerate(ps):
+        check_generated(dirs, "wide", torch.bfloat16, p, [s[b] for s in out], f"streaming products, sequence {b}")
+    from dryft_b200.ops import kernels as K
+    K.check_error_flags()
+    assert int(K.gemm_stream_scratch(eng.device)[1].abs().sum()) == 0
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
