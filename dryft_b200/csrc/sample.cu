@@ -42,10 +42,32 @@ __global__ void __launch_bounds__(THREADS) argmax_rows_kernel(const float* __res
   const float* lg = logits + (size_t)r * row_stride;
   float best = -INFINITY;
   int idx = 0x7fffffff;
-  for (int i = threadIdx.x; i < vocab; i += THREADS) {
-    const float v = lg[i];
+  auto take = [&](float v, int i) {
     if (v > best || (v == best && i < idx) || idx == 0x7fffffff) { best = v; idx = i; }
+  };
+  // 16-byte loads, four of them in flight per thread, where the row allows; a thread sees its indices in rising order
+  int done = 0;
+  if ((reinterpret_cast<uintptr_t>(lg) & 15) == 0) {
+    const float4* lg4 = reinterpret_cast<const float4*>(lg);
+    const int n4 = vocab / 4;
+    int i = threadIdx.x;
+    for (; i + 3 * THREADS < n4; i += 4 * THREADS) {
+      float4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) v[u] = lg4[i + u * THREADS];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int b = 4 * (i + u * THREADS);
+        take(v[u].x, b); take(v[u].y, b + 1); take(v[u].z, b + 2); take(v[u].w, b + 3);
+      }
+    }
+    for (; i < n4; i += THREADS) {
+      const float4 v = lg4[i];
+      take(v.x, 4 * i); take(v.y, 4 * i + 1); take(v.z, 4 * i + 2); take(v.w, 4 * i + 3);
+    }
+    done = n4 * 4;
   }
+  for (int i = done + threadIdx.x; i < vocab; i += THREADS) take(lg[i], i);
   // (value desc, index asc) reduction
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {

@@ -39,6 +39,8 @@ class Stepper:
         # query tokens per prefill tile: the smallest any mixer asks for (64 unless every mixer takes more)
         self.prefill_tile = min([getattr(b.mixer, "prefill_tile", 64) for b in model.blocks] or [64])
         self.last_decode_slots: Optional[torch.Tensor] = None
+        self._prompt_graphs: Dict[tuple, "_PromptGraph"] = {}   # (tokens, sequences, wanted rows, tiles) -> captured step
+        self._prompt_shapes_seen: set = set()
 
     # ------------------------------------------------------------------ host -> device metadata
     def step(self, slots: Sequence[int], tokens: Sequence[Sequence[int]], want: Sequence[Sequence[int]]) -> Optional[torch.Tensor]:
@@ -94,7 +96,45 @@ class Stepper:
         T = len(tiles0)
         W = len(rows)
         packed = np.concatenate((flat, np.asarray(cu + list(slots) + rows + tiles0 + tilesn, dtype=np.int64))).astype(np.int32)
-        dev = self._upload(packed)
+        max_kv = max(st + q for st, q in zip(starts, q_lens))
+        logits = None
+        shape = (N, B, W, T)
+        if self.cuda_graphs and not decode and N >= self.PROMPT_GRAPH_MIN_TOKENS:
+            # A prompt step's launches depend on these four counts only (every length, position, slot and tile is
+            # data the kernels read on the device), so a step of a shape seen before is replayed from a captured
+            # graph: the host's lead before the first launch and the gaps between some hundred launches go away.
+            g = self._prompt_graphs.get(shape)
+            if g is not None:
+                self._prompt_graphs[shape] = self._prompt_graphs.pop(shape)     # most recently used last
+                self._upload(packed, into=g.ints)
+                logits = g.replay()
+            elif shape in self._prompt_shapes_seen:                             # second time: worth a capture
+                g = _PromptGraph(self, shape, int(packed.size))
+                self._upload(packed, into=g.ints)
+                g.capture()
+                logits = g.replay()
+                self._prompt_graphs[shape] = g
+                while len(self._prompt_graphs) > self.PROMPT_GRAPHS_KEPT:       # each holds its activations: keep a few
+                    self._prompt_graphs.pop(next(iter(self._prompt_graphs)))
+            else:
+                self._prompt_shapes_seen.add(shape)
+                g = None
+        else:
+            g = None
+        if g is None:
+            dev = self._upload(packed)
+            meta = torch.empty(2 * N, dtype=torch.int32, device=self.rt.device)
+            logits = self._run(dev, meta, shape, decode, max_kv)
+        for s, q in zip(slots, q_lens):
+            self.cache.advanced(s, q)
+        return logits
+
+    PROMPT_GRAPH_MIN_TOKENS = 256   # below this a step is too short for its launches to matter
+    PROMPT_GRAPHS_KEPT = 4
+
+    def _run(self, dev: torch.Tensor, meta: torch.Tensor, shape, decode: bool, max_kv: int) -> Optional[torch.Tensor]:
+        """The device side of a step: ``dev`` holds the step's integers as ``step`` packs them."""
+        N, B, W, T = shape
         o = 0
         d_tokens = dev[o:o + N]; o += N
         d_cu = dev[o:o + B + 1]; o += B + 1
@@ -102,20 +142,18 @@ class Stepper:
         d_rows = dev[o:o + W]; o += W
         d_t0 = dev[o:o + T]; o += T
         d_tn = dev[o:o + T]; o += T
-        meta = torch.empty(2 * N, dtype=torch.int32, device=self.rt.device)
         tok_slot, tok_pos = meta[:N], meta[N:]
         K.step_meta(d_cu, d_slot, self.cache.seq_len, tok_slot, tok_pos, N, B)
         ctx = StepContext(n_tokens=N, n_seqs=B, tokens=d_tokens, cu_q=d_cu, seq_slot=d_slot, tok_slot=tok_slot,
-                          tok_pos=tok_pos, decode=decode, max_kv=max(st + q for st, q in zip(starts, q_lens)),
+                          tok_pos=tok_pos, decode=decode, max_kv=max_kv,
                           tile_tok0=d_t0 if T else None, tile_rows=d_tn if T else None, n_tiles=T, tile_size=self.prefill_tile)
         logits = self.model.forward(ctx, self.cache, d_rows if W else None, W)
         K.step_advance(d_cu, d_slot, self.cache.seq_len, B)
-        for s, q in zip(slots, q_lens):
-            self.cache.advanced(s, q)
         return logits
 
-    def _upload(self, ints: np.ndarray) -> torch.Tensor:
-        """One host->device copy of the step's integers (an int32 array) through pinned memory."""
+    def _upload(self, ints: np.ndarray, into: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """One host->device copy of the step's integers (an int32 array) through pinned memory, into a fresh device
+        tensor or into ``into`` (a captured graph's own buffer)."""
         n = int(ints.size)
         if self._pinned is None or self._pinned.numel() < n:
             self._pinned = torch.empty(max(n, 4096), dtype=torch.int32, pin_memory=True)
@@ -124,7 +162,7 @@ class Stepper:
             self._upload_event.synchronize()
         buf = self._pinned[:n]
         buf.numpy()[:] = ints
-        dev = torch.empty(n, dtype=torch.int32, device=self.rt.device)
+        dev = torch.empty(n, dtype=torch.int32, device=self.rt.device) if into is None else into[:n]
         dev.copy_(buf, non_blocking=True)
         self._upload_event = torch.cuda.Event()
         self._upload_event.record()
@@ -154,6 +192,36 @@ class Stepper:
             self.cache.advanced(s, 1)
         self.last_decode_slots = g.seq_slot  # int32 [bucket] on the device, -1 for padding rows
         return logits
+
+
+class _PromptGraph:
+    """A captured prompt step of one shape: its own copy of the step's integers, its token metadata and the graph.
+    The reference captures decode steps only (``engine/dryft_qwen3/graphs.py:25-59``); its prompts run eagerly."""
+
+    def __init__(self, stepper: Stepper, shape, n_ints: int):
+        self.st = stepper
+        self.shape = shape
+        dev = stepper.rt.device
+        self.ints = torch.zeros(n_ints, dtype=torch.int32, device=dev)
+        self.meta = torch.empty(2 * shape[0], dtype=torch.int32, device=dev)
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+        self.n_kernels = 0
+
+    def capture(self) -> None:
+        """The eager run of this shape that came before was the warm-up (library workspaces, kernel attributes)."""
+        torch.cuda.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        before = K.launch_count
+        with torch.cuda.graph(self.graph):
+            self.logits = self.st._run(self.ints, self.meta, self.shape, False, 0)
+        self.n_kernels = K.launch_count - before
+
+    def replay(self) -> Optional[torch.Tensor]:
+        self.graph.replay()
+        K.launch_count += self.n_kernels
+        # the graph writes its logits in place: hand out a copy, the next replay must not change what a caller keeps
+        return None if self.logits is None else self.logits.clone()
 
 
 def _bucket(b: int) -> int:

@@ -333,3 +333,37 @@ def test_more_than_eight_attention_splits(dirs, dtype):
     check(torch.cat(rows), dirs, "long", dtype, toks, list(range(n - 1, n + 4)), "8,200 keys, captured graph")
     from dryft_b200.ops import kernels as K
     K.check_error_flags()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_prompt_steps_replayed_from_a_captured_graph(dirs, dtype):
+    """A prompt step's launches depend only on (tokens, sequences, wanted rows, tiles): the second step of a shape is
+    captured, later ones are replayed with other tokens, other lengths (300 + 100, then 110 + 290: the same counts),
+    other slots and other starting positions (a chunk continuing a sequence).  Every result is compared with the
+    plain implementation; results handed out earlier must not change when the graph runs again."""
+    eng = engine(dirs, "long", dtype, max_batch=24, max_seq_len=9000, max_tokens=9000 + 23 * 256)
+    assert eng.stepper.cuda_graphs
+    kept = []
+    cases = [(300, 100), (300, 100), (110, 290), (256, 144), (300, 100)]
+    for i, (a, b) in enumerate(cases):
+        ps = prompts("long", [a, b], 90 + i)
+        slots = eng.cache.open_sequences(2 + i % 2)[-2:]          # other slots from one step to the next
+        got = step(eng, slots, ps, [[a - 1, 0], [b - 1]])
+        kept.append((got, got.clone(), ps))
+        eng.cache.close_sequences([s for s in range(eng.cache.max_slots) if eng.cache.slots.is_held(s)])
+        check(got[:2], dirs, "long", dtype, ps[0], [a - 1, 0], f"prompt graph, case {i}, first sequence")
+        check(got[2:], dirs, "long", dtype, ps[1], [b - 1], f"prompt graph, case {i}, second sequence")
+    tile = eng.stepper.prefill_tile
+    assert (400, 2, 3, -(-300 // tile) + -(-100 // tile)) in eng.stepper._prompt_graphs
+    for got, copy, _ in kept:
+        assert torch.equal(got, copy), "a later replay changed logits handed out earlier"
+    # a chunk that continues two sequences (positions 64.. and 10..): again 400 tokens, 2 sequences, 3 rows, 4 tiles
+    ps = prompts("long", [64 + 300, 10 + 100], 99)
+    slots = eng.cache.open_sequences(2)
+    step(eng, slots, [ps[0][:64], ps[1][:10]], [[], []])
+    got = step(eng, slots, [ps[0][64:], ps[1][10:]], [[299, 0], [99]])
+    eng.cache.close_sequences(slots)
+    check(got[:2], dirs, "long", dtype, ps[0], [363, 64], "prompt graph, continued chunk, first sequence")
+    check(got[2:], dirs, "long", dtype, ps[1], [109], "prompt graph, continued chunk, second sequence")
+    eng.cache.check()
+    assert eng.cache.slots.n_held == 0
