@@ -32,23 +32,37 @@ class PartSpec:
 
 
 @dataclass(frozen=True)
+class ExtraPart:
+    """A part of a layer beyond the usual four: ``family`` says which registry builds it ("norm", "ffn" or
+    "mixer"), ``name`` is what the block arrangement knows it by (a norm behind the mixer's output, say)."""
+
+    name: str
+    family: str
+    spec: PartSpec
+    prefix: str
+
+
+@dataclass(frozen=True)
 class LayerSpec:
     """One layer: an arrangement (``block``) of a mixer, a feed-forward and their norms.
 
     The ``*_prefix`` fields are the checkpoint name prefixes of the four parts
     (``model.layers.3.self_attn.``); each part appends its own local tensor names
-    (``q_proj.weight``), so no part carries an architecture's naming.
+    (``q_proj.weight``), so no part carries an architecture's naming.  A layer without a feed-forward
+    leaves ``ffn`` and ``norm_ffn`` ``None``; a layer with more parts (norms on both sides of a part, a
+    second feed-forward) lists them in ``extra``, and its block arrangement is handed them by name.
     """
 
     block: str
     mixer: PartSpec
-    ffn: PartSpec
+    ffn: Optional[PartSpec]
     norm_mixer: PartSpec
-    norm_ffn: PartSpec
+    norm_ffn: Optional[PartSpec]
     mixer_prefix: str
     ffn_prefix: str
     norm_mixer_prefix: str
     norm_ffn_prefix: str
+    extra: Tuple[ExtraPart, ...] = ()
 
 
 @dataclass(frozen=True)
@@ -85,6 +99,15 @@ class ModelSpec:
             raise ValueError("model spec has no layers")
         if not self.schedule:
             raise ValueError("model spec has an empty run order")
+        for i, layer in enumerate(self.layers):
+            if (layer.ffn is None) != (layer.norm_ffn is None):
+                raise ValueError(f"layer {i}: a feed-forward and its norm go together (one of them is missing)")
+            names = [e.name for e in layer.extra]
+            if len(set(names)) != len(names):
+                raise ValueError(f"layer {i}: two extra parts share a name: {names}")
+            for e in layer.extra:
+                if e.family not in ("norm", "ffn", "mixer"):
+                    raise ValueError(f"layer {i}: extra part {e.name!r} has family {e.family!r}; known: norm, ffn, mixer")
         for i, st in enumerate(self.schedule):
             if not 0 <= st.layer < len(self.layers):
                 raise ValueError(f"run step {i} names layer {st.layer}, but there are {len(self.layers)} layers")

@@ -15,7 +15,7 @@ import torch
 
 from ..cache.store import KVNeed, SequenceCache, StateNeed
 from ..config.spec import ModelSpec
-from ..parts.base import BLOCKS, EMBEDDINGS, FFNS, HEADS, MIXERS, NORMS, Residual, Runtime, StepContext
+from ..parts.base import BLOCKS, EMBEDDINGS, FAMILIES, FFNS, HEADS, MIXERS, NORMS, Residual, Runtime, StepContext
 
 
 class DecoderModel:
@@ -30,9 +30,13 @@ class DecoderModel:
         for layer in spec.layers:
             norm_mixer = NORMS.get(layer.norm_mixer.kind)(layer.norm_mixer.params, layer.norm_mixer_prefix, weights, rt)
             mixer = MIXERS.get(layer.mixer.kind)(layer.mixer.params, layer.mixer_prefix, weights, rt)
-            norm_ffn = NORMS.get(layer.norm_ffn.kind)(layer.norm_ffn.params, layer.norm_ffn_prefix, weights, rt)
-            ffn = FFNS.get(layer.ffn.kind)(layer.ffn.params, layer.ffn_prefix, weights, rt)
-            self.blocks.append(BLOCKS.get(layer.block)(norm_mixer, mixer, norm_ffn, ffn))
+            norm_ffn = ffn = None
+            if layer.ffn is not None:
+                norm_ffn = NORMS.get(layer.norm_ffn.kind)(layer.norm_ffn.params, layer.norm_ffn_prefix, weights, rt)
+                ffn = FFNS.get(layer.ffn.kind)(layer.ffn.params, layer.ffn_prefix, weights, rt)
+            extra = {e.name: FAMILIES[e.family].get(e.spec.kind)(e.spec.params, e.prefix, weights, rt) for e in layer.extra}
+            make = BLOCKS.get(layer.block)
+            self.blocks.append(make(norm_mixer, mixer, norm_ffn, ffn, extra=extra) if extra else make(norm_mixer, mixer, norm_ffn, ffn))
         self.final_norm = NORMS.get(spec.final_norm.kind)(spec.final_norm.params, spec.final_norm_prefix, weights, rt)
         self.head = HEADS.get(spec.head.kind)(spec.head.params, spec.head_prefix, weights, rt, embedding=self.embedding)
 
@@ -57,8 +61,9 @@ class DecoderModel:
                         total += v.numel() * v.element_size()
         visit(self.embedding); visit(self.final_norm); visit(self.head)
         for b in self.blocks:
-            for part in (b.norm_mixer, b.mixer, b.norm_ffn, b.ffn):
-                visit(part)
+            for part in (b.norm_mixer, b.mixer, b.norm_ffn, b.ffn, *getattr(b, "extra", {}).values()):
+                if part is not None:
+                    visit(part)
         return total
 
     def forward(self, ctx: StepContext, cache: SequenceCache, want_rows: Optional[torch.Tensor], n_want: int,

@@ -14,7 +14,8 @@ position    ``__init__(params, head_dim, rt)``; gives ``rotary_dim`` and ``inv_f
 mixer       ``tensors``; ``__init__``; ``kv_need()`` / ``state_need()``;
             ``forward(h, ctx, cache, state, owns_cache)`` -> ``[tokens, hidden]`` (not yet added).
 ffn         ``tensors``; ``__init__``; ``forward(h, ctx)`` -> ``[tokens, hidden]``.
-block       ``__init__(norm_mixer, mixer, norm_ffn, ffn)``;
+block       ``__init__(norm_mixer, mixer, norm_ffn, ffn)`` (``norm_ffn`` and ``ffn`` are None in a layer without a
+            feed-forward; a layer that lists extra parts also passes ``extra={name: part}``);
             ``forward(res, ctx, cache, state, owns_cache)`` -> ``Residual``: the stream, plus either the
             not-yet-added output of the block's last part (so the next norm can fuse the add) or the
             stream's sums of squares (so the next fused product can normalise it).
@@ -152,6 +153,8 @@ POSITIONS = Registry("position encoding")
 BLOCKS = Registry("block arrangement")
 EMBEDDINGS = Registry("embedding")
 HEADS = Registry("output head")
+
+FAMILIES = {"mixer": MIXERS, "ffn": FFNS, "norm": NORMS}   # the registries a layer's extra parts are built from
 
 register_mixer = MIXERS.register
 register_ffn = FFNS.register

@@ -5,6 +5,7 @@
     a  = mixer(h)                               not-yet-added feed-forward output)
     x += a        ; h = norm_ffn(x)            (one fused kernel)
     delta_out = ffn(h)
+A layer without a feed-forward stops after the mixer and returns its output as ``delta_out``.
 The block returns the stream and ``delta_out``: the add of ``delta_out`` is left to whatever norm comes
 next (the next block's, or the final norm), which is how the reference fuses "residual add + next
 norm".  With few rows (decode) and parts that offer it, the norms, the adds and the activation are
@@ -32,6 +33,8 @@ class PreNormBlock:
 
     def _fusable(self, n_rows: int) -> bool:
         m, f = self.mixer, self.ffn
+        if f is None:
+            return False
         return (hasattr(m, "forward_normed") and hasattr(f, "forward_normed")
                 and m.can_fuse(n_rows, self.norm_mixer) and f.can_fuse(n_rows, self.norm_ffn))
 
@@ -72,5 +75,7 @@ class PreNormBlock:
             return Residual(x, None, ss, parts, xw, next_norm if xw is not None else None)
         h = self.norm_mixer.forward(x) if res.delta is None else self.norm_mixer.add_forward(x, res.delta)
         a = self.mixer.forward(h, ctx, cache, state, owns_cache)
+        if self.ffn is None:           # a layer without a feed-forward: the mixer's output is what the next norm adds
+            return Residual(x, a)
         h = self.norm_ffn.add_forward(x, a)
         return Residual(x, self.ffn.forward(h, ctx))

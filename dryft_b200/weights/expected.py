@@ -5,7 +5,7 @@ from __future__ import annotations
 from typing import Dict
 
 from ..config.spec import ModelSpec
-from ..parts.base import EMBEDDINGS, FFNS, HEADS, MIXERS, NORMS, TensorInfo
+from ..parts.base import EMBEDDINGS, FAMILIES, FFNS, HEADS, MIXERS, NORMS, TensorInfo
 
 
 def expected_tensors(spec: ModelSpec) -> Dict[str, TensorInfo]:
@@ -21,8 +21,11 @@ def expected_tensors(spec: ModelSpec) -> Dict[str, TensorInfo]:
     for layer in spec.layers:
         add(NORMS.get(layer.norm_mixer.kind).tensors(layer.norm_mixer.params, layer.norm_mixer_prefix))
         add(MIXERS.get(layer.mixer.kind).tensors(layer.mixer.params, layer.mixer_prefix))
-        add(NORMS.get(layer.norm_ffn.kind).tensors(layer.norm_ffn.params, layer.norm_ffn_prefix))
-        add(FFNS.get(layer.ffn.kind).tensors(layer.ffn.params, layer.ffn_prefix))
+        if layer.ffn is not None:
+            add(NORMS.get(layer.norm_ffn.kind).tensors(layer.norm_ffn.params, layer.norm_ffn_prefix))
+            add(FFNS.get(layer.ffn.kind).tensors(layer.ffn.params, layer.ffn_prefix))
+        for e in layer.extra:
+            add(FAMILIES[e.family].get(e.spec.kind).tensors(e.spec.params, e.prefix))
     add(NORMS.get(spec.final_norm.kind).tensors(spec.final_norm.params, spec.final_norm_prefix))
     add(HEADS.get(spec.head.kind).tensors(spec.head.params, spec.head_prefix))
     return out

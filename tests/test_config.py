@@ -143,3 +143,26 @@ def test_run_order_is_validated():
         replace(spec, schedule=(RunStep(0, cache_from=0),)).validate()
     with pytest.raises(ValueError):
         replace(spec, schedule=(RunStep(0), RunStep(1, cache_from=0), RunStep(1, cache_from=1))).validate()
+
+
+def test_layer_spec_checks_its_optional_and_extra_parts():
+    from dryft_b200.config import ExtraPart, LayerSpec, ModelSpec, PartSpec, RunStep
+
+    norm = PartSpec("rmsnorm", {"size": 8, "eps": 1e-6})
+    mixer = PartSpec("attention", {})
+    ffn = PartSpec("swiglu", {})
+
+    def spec(layer):
+        return ModelSpec("X", 10, 8, 16, PartSpec("embedding", {}), (layer,), (RunStep(0),), norm, PartSpec("lm_head", {}))
+
+    spec(LayerSpec("prenorm", mixer, None, norm, None, "a.", "", "n.", "")).validate()             # no feed-forward
+    spec(LayerSpec("prenorm", mixer, ffn, norm, norm, "a.", "f.", "n.", "m.",
+                   extra=(ExtraPart("post", "norm", norm, "p."),))).validate()
+    with pytest.raises(ValueError, match="go together"):
+        spec(LayerSpec("prenorm", mixer, ffn, norm, None, "a.", "f.", "n.", "")).validate()
+    with pytest.raises(ValueError, match="share a name"):
+        spec(LayerSpec("prenorm", mixer, ffn, norm, norm, "a.", "f.", "n.", "m.",
+                       extra=(ExtraPart("post", "norm", norm, "p."), ExtraPart("post", "norm", norm, "q.")))).validate()
+    with pytest.raises(ValueError, match="family"):
+        spec(LayerSpec("prenorm", mixer, ffn, norm, norm, "a.", "f.", "n.", "m.",
+                       extra=(ExtraPart("post", "table", norm, "p."),))).validate()

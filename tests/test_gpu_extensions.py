@@ -259,3 +259,108 @@ def test_a_seed_names_one_model_wherever_it_is_drawn(tmp_path):
     assert H.rel_err(outs[1], P.load_plain(d, torch.float32).logits(toks)) <= H.FP32_TOL
     with pytest.raises(ValueError):
         Engine.from_config(cfg, seed=1, draw_on="host", **kw)
+
+
+def test_layers_of_other_shapes_need_no_change_to_the_library():
+    """Two layer shapes that are not (norm, mixer, norm, feed-forward), in one toy architecture: a layer with a
+    norm on both sides of each part (two extra norms, listed in the layer's ``extra`` and handed to a block
+    arrangement registered here) and a layer without a feed-forward (the stock arrangement with ``ffn=None``).
+    Whole prompts, token by token, two sequences in a batch, and a plain evaluation written out here agree."""
+    from dryft_b200.config import ExtraPart, LayerSpec, ModelSpec, PartSpec, RunStep, register_architecture, unregister_architecture
+    from dryft_b200.engine.api import Engine
+    from dryft_b200.parts import BLOCKS, register_block
+    from dryft_b200.parts.base import Residual
+
+    class SandwichBlock:
+        """x += post_m(mixer(pre_m(x)));  x += post_f(ffn(pre_f(x)))"""
+
+        def __init__(self, norm_mixer, mixer, norm_ffn, ffn, extra):
+            self.norm_mixer, self.mixer, self.norm_ffn, self.ffn = norm_mixer, mixer, norm_ffn, ffn
+            self.extra = extra
+
+        def forward(self, res, ctx, cache, state, owns_cache=True):
+            x = res.x
+            if res.delta is not None:
+                x = (x.float() + res.delta.float()).to(x.dtype)
+            a = self.extra["post_mixer"].forward(self.mixer.forward(self.norm_mixer.forward(x), ctx, cache, state, owns_cache))
+            x = (x.float() + a.float()).to(x.dtype)
+            f = self.extra["post_ffn"].forward(self.ffn.forward(self.norm_ffn.forward(x), ctx))
+            return Residual((x.float() + f.float()).to(x.dtype))
+
+    Hd, V, D = 48, 101, 16
+
+    class ToyConfig:
+        def __init__(self, raw):
+            self.raw = dict(raw)
+
+        def to_dict(self):
+            return dict(self.raw)
+
+        def model_spec(self):
+            norm = PartSpec("rmsnorm", {"size": Hd, "eps": 1e-5})
+            attn = PartSpec("attention", {"hidden_size": Hd, "num_heads": 3, "num_kv_heads": 1, "head_dim": D, "scale": 0.25,
+                                          "window": None, "qk_norm": None, "position": PartSpec("rope", {"rotary_dim": D, "theta": 1e4})})
+            ffn = PartSpec("swiglu", {"hidden_size": Hd, "intermediate_size": 64})
+            sandwich = LayerSpec("toy_sandwich", attn, ffn, norm, norm, "l0.attn.", "l0.ffn.", "l0.pre_m.", "l0.pre_f.",
+                                 extra=(ExtraPart("post_mixer", "norm", norm, "l0.post_m."), ExtraPart("post_ffn", "norm", norm, "l0.post_f.")))
+            no_ffn = LayerSpec("prenorm", attn, None, norm, None, "l1.attn.", "", "l1.n.", "")
+            usual = LayerSpec("prenorm", attn, ffn, norm, norm, "l2.attn.", "l2.ffn.", "l2.n1.", "l2.n2.")
+            return ModelSpec("ToyShapesForCausalLM", V, Hd, 256, PartSpec("embedding", {"vocab_size": V, "hidden_size": Hd}),
+                             (sandwich, no_ffn, usual), tuple(RunStep(i) for i in range(3)), norm,
+                             PartSpec("lm_head", {"vocab_size": V, "hidden_size": Hd, "tied": True}),
+                             embedding_prefix="emb.", final_norm_prefix="fn.", head_prefix="head.")
+
+    register_block("toy_sandwich", SandwichBlock)
+    register_architecture("ToyShapesForCausalLM", ToyConfig)
+    try:
+        eng = Engine.from_config({"architectures": ["ToyShapesForCausalLM"]}, seed=11, std=0.2, dtype="float32", max_batch=2,
+                                 max_seq_len=128, max_tokens=256)
+        n = 26
+        toks = torch.randint(0, V, (n,), generator=torch.Generator().manual_seed(3)).tolist()
+        with torch.inference_mode():
+            s = eng.cache.open_sequences(1)
+            whole = eng.stepper.step(s, [toks], [list(range(n))]).cpu()
+            eng.cache.close_sequences(s)
+            s = eng.cache.open_sequences(1)
+            parts = [eng.stepper.step(s, [toks[:9]], [list(range(9))]).cpu()]
+            for t in toks[9:]:
+                parts.append(eng.stepper.step(s, [[t]], [[0]]).cpu())
+            eng.cache.close_sequences(s)
+            s = eng.cache.open_sequences(2)
+            both = eng.stepper.step(s, [toks[:4], toks], [[3], list(range(n))]).cpu()
+            eng.cache.close_sequences(s)
+        assert torch.isfinite(whole).all()
+        assert H.rel_err(torch.cat(parts), whole) <= H.FP32_TOL
+        assert H.rel_err(both[1:], whole) <= H.FP32_TOL and H.rel_err(both[:1], whole[3:4]) <= H.FP32_TOL
+        assert eng.generate_many([toks[:5]], 4)[0] == [int(t) for t in eng.generate_many([toks[:5]], 4)[0]]
+
+        # plain evaluation from the engine's own tensors
+        m = eng.model
+        x = P.embed(torch.tensor(toks), m.embedding.table.float().cpu(), torch.float32)
+        pos = torch.arange(n)
+
+        def attend(at, h):
+            qkv = h @ at.w_qkv.float().cpu().T
+            q, k, v = qkv.split([3 * D, D, D], dim=-1)
+            q, k, v = q.view(n, 3, D), k.view(n, 1, D), v.view(n, 1, D)
+            cos, sin = P.rope_cos_sin(pos, D, 1e4, torch.float32)
+            o = P.causal_attention(P.apply_rope(q, cos, sin), P.apply_rope(k, cos, sin), v, 0.25, None, torch.float32)
+            return o @ at.w_o.float().cpu().T
+
+        def feed(ff, h):
+            gu = h @ ff.w_gate_up.float().cpu().T
+            return P.silu_mul(gu[:, :64], gu[:, 64:]) @ ff.w_down.float().cpu().T
+
+        nrm = lambda part, t: P.rmsnorm(t, part.weight.cpu(), 1e-5)
+        b0, b1, b2 = m.blocks
+        x = x + nrm(b0.extra["post_mixer"], attend(b0.mixer, nrm(b0.norm_mixer, x)))
+        x = x + nrm(b0.extra["post_ffn"], feed(b0.ffn, nrm(b0.norm_ffn, x)))
+        assert b1.ffn is None and b1.norm_ffn is None
+        x = x + attend(b1.mixer, nrm(b1.norm_mixer, x))
+        x = x + attend(b2.mixer, nrm(b2.norm_mixer, x))
+        x = x + feed(b2.ffn, nrm(b2.norm_ffn, x))
+        logits = nrm(m.final_norm, x) @ m.head.weight.float().cpu().T
+        assert H.rel_err(whole, logits) <= 5 * H.FP32_TOL
+    finally:
+        BLOCKS.unregister("toy_sandwich")
+        unregister_architecture("ToyShapesForCausalLM")
