@@ -9,15 +9,16 @@
 //   norm prologue (kernels/rmsnorm.py:21-39), residual epilogue with sums of squares for the next
 //   norm (rmsnorm.py:34), SiLU*mul epilogue (kernels/silu_mul.py:29-32; weights.py:98-100).
 //
-// A block of 8 warps takes 16 rows of W at a time; blocks are persistent, at most two per SM, each
-// walking over every grid-th tile.  The warps split K into 8 equal ranges.  A warp requests its whole
+// A block of 8 warps takes 16 rows of W at a time; blocks are persistent, two per SM (one where the
+// staged activations are too large for two), each walking over every grid-th tile.  The warps split K into 8 equal ranges.  A warp requests its whole
 // share of the tile's 16 rows at once — K/128 16-byte loads per thread that bypass L1, all in flight
 // together — then feeds them to mma.sync.m16n8k16 with W as the 16 x 16 operand and 8 batch rows as
 // the 16 x 8 operand (the k index permuted identically in both operands, so that a thread's fragment
 // is one contiguous 16-byte piece).  While a warp consumes, the other fifteen on the SM have their
 // requests in flight.  With the norm prologue the normalised activations are made once per block and
-// stay in shared memory; otherwise they are read through L1.  The 8 partial sums are added in warp
-// order through shared memory: a row's result depends neither on the other rows nor on M.
+// stay in shared memory (the M rows there are and one row of zeros for the rest of the operand);
+// otherwise they are read through L2.  The 8 partial sums are added in warp order through shared
+// memory: a row's result depends neither on the other rows nor on M.
 //
 // The norm can also be split between two launches, which takes it off the consumer's critical path: a
 // residual product that knows the next norm's weight w leaves, beside the new stream x, the weighted
@@ -48,6 +49,18 @@ constexpr int N_CHUNKS = (SPW + CHUNK - 1) / CHUNK;
 constexpr int SS_STRIDE = 64;
 constexpr int KA = K + ((64 - (K * 2) % 128 + 128) % 128) / 2;  // resident row stride: bytes = 64 mod 128
 
+// Shared memory and L1 are one 256 KB array per SM, cut at one of a few places, and the weights on their way
+// into registers are held in L1: an SM streams at full rate only while the L1 that the cut leaves is about as
+// large as the bytes its blocks keep in flight (two blocks: 160 KB).  Measured on the gate|up product of a
+// 5,120-wide model (524 MB): 80 us with 10 KB of shared memory a block, 162 us with 101 KB (two blocks: the
+// 228 KB cut), 83 us with 126 KB (one block an SM, the 132 KB cut).  So every instantiation asks for the
+// 100 KB cut (also so that neighbouring launches, which overlap, agree on it: a batch-8 step of a 2,560-wide
+// model takes 2.12 ms this way, 2.26 ms when each launch is left to the driver's choice), stages only the rows
+// there are, and runs one block an SM where two would not fit under that cut.
+constexpr int CARVEOUT_PCT = 43;
+constexpr size_t CARVEOUT_BYTES = 100 * 1024;
+constexpr size_t SMEM_MOST = 164 * 1024;   // one block under the 164 KB cut: L1 still holds one block's requests
+
 enum Mode { STORE_BF16 = 0, STORE_F32 = 1, RESIDUAL = 2, SILU = 3 };
 // what happens to the activations: nothing; RMSNorm in the prologue (rows normalised into shared memory);
 // or they come weighted already (T(x * w)) and the sums are scaled by inv[m] in the epilogue
@@ -68,18 +81,26 @@ __device__ __forceinline__ float bfr(float v) { return __bfloat162float(__float2
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// bytes of the partial sums, which also hold the norm's weight while the activations are normalised
+template <int MB, int PRO> __host__ __device__ constexpr size_t head_bytes() {
+  const size_t red = (size_t)WARPS * ROWS * (8 * MB + 1) * 4, nw = PRO == NORMED ? (size_t)K * 2 : 0;
+  return ((red > nw ? red : nw) + 15) / 16 * 16;
+}
+
 template <int MB, int MODE, int PRO>
 __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
     const bf16* __restrict__ A, int lda, const bf16* __restrict__ W, void* C, int ldc, int M, int N,
     const float* __restrict__ norm_w, const float* __restrict__ ss_in, int ss_parts, float eps, float* __restrict__ ss_out,
-    const float* __restrict__ next_w, bf16* __restrict__ xw_out) {
+    const float* __restrict__ next_w, bf16* __restrict__ xw_out, int rs) {
   constexpr bool NORM = PRO == NORMED;
   constexpr int MP = 8 * MB;
   constexpr int RED = WARPS * ROWS * (MP + 1);
   extern __shared__ __align__(16) unsigned char smem[];
-  // two buffers of [WARPS][ROWS][MP + 1] partial sums, 64 floats of inv, then the resident activations
-  float* red_base = reinterpret_cast<float*>(smem);
-  float* inv_s = red_base + 2 * RED;
+  // [WARPS][ROWS][MP + 1] partial sums (the norm's weight lies in the same bytes until the first tile is
+  // reduced), 64 floats of inv, then the resident activations: the rs = min(M, MP) rows there are, and one
+  // row of zeros behind them that stands for every row from M on
+  float* red = reinterpret_cast<float*>(smem);
+  float* inv_s = reinterpret_cast<float*>(smem + head_bytes<MB, PRO>());
   bf16* a_res = reinterpret_cast<bf16*>(inv_s + SS_STRIDE);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
@@ -117,7 +138,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
     request(w0, w1, 0);  // weights depend on no earlier launch
   }
 
-  bf16* nw_s = a_res + (size_t)MP * KA;   // the norm's weight as bfloat16 (its values are bfloat16 values held in 32-bit)
+  bf16* nw_s = reinterpret_cast<bf16*>(smem);   // the norm's weight as bfloat16 (its values are bfloat16 values held in 32-bit)
   if (NORM) {
     // the norm's weight depends on no earlier launch either: into shared memory before the wait
     for (int i = tid; i < K / 4; i += THREADS) {
@@ -148,22 +169,23 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
     // the weighted activations go to shared memory once per block (one trip through L2, no arithmetic):
     // every tile of the block reads them from there
     constexpr int CHUNKS = K / 8;
-    constexpr int ITEMS = MP * CHUNKS;
-    constexpr int PER = ITEMS / THREADS;
-    constexpr int BATCH = PER <= 10 ? PER : 10;   // one trip for eight rows of up to 2,560
+    constexpr int BATCH = 5;    // pieces a thread requests together (registers also hold the first weights)
+    const int items = rs * CHUNKS;
+    if (rs < MP)
+      for (int c = tid; c < CHUNKS; c += THREADS) *reinterpret_cast<uint4*>(a_res + (size_t)rs * KA + c * 8) = zero;
 #pragma unroll 1
-    for (int first = 0; first < PER; first += BATCH) {
+    for (int first = tid; first < items; first += BATCH * THREADS) {
       uint4 raw[BATCH];
 #pragma unroll
       for (int u = 0; u < BATCH; ++u) {
-        const int i = tid + (first + u) * THREADS;
+        const int i = first + u * THREADS;
         const int m = i / CHUNKS, c = i - m * CHUNKS;
-        raw[u] = (first + u < PER && m < M) ? ld_prev(reinterpret_cast<const uint4*>(A + (size_t)m * lda + c * 8)) : zero;
+        raw[u] = i < items ? ld_prev(reinterpret_cast<const uint4*>(A + (size_t)m * lda + c * 8)) : zero;
       }
 #pragma unroll
       for (int u = 0; u < BATCH; ++u) {
-        if (first + u >= PER) break;
-        const int i = tid + (first + u) * THREADS;
+        const int i = first + u * THREADS;
+        if (i >= items) break;
         const int m = i / CHUNKS, c = i - m * CHUNKS;
         *reinterpret_cast<uint4*>(a_res + (size_t)m * KA + c * 8) = raw[u];
       }
@@ -176,21 +198,21 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
     // then the normalised rows a[m,k] = T(T(x[m,k] * inv[m]) * w[k]) go to shared memory once per block.
     // The activations are requested together with the sums of squares, a batch of loads per thread
     // at once, so that the whole prologue is one or two trips to memory.
-    constexpr int CHUNKS = K / 8;
-    constexpr int ITEMS = MP * CHUNKS;            // 16-byte pieces of the activations; ITEMS % THREADS == 0
-    constexpr int PER = ITEMS / THREADS;          // pieces per thread
-    constexpr int BATCH = PER <= 5 ? PER : 5;     // pieces a thread requests together (registers also hold the first weights)
-    static_assert(ITEMS % THREADS == 0, "K is a multiple of 256");
+    constexpr int CHUNKS = K / 8;                 // 16-byte pieces of a row
+    constexpr int BATCH = 5;                      // pieces a thread requests together (registers also hold the first weights)
+    const int items = rs * CHUNKS;
     uint4 raw[BATCH];
     auto fetch = [&](int first) {
 #pragma unroll
       for (int u = 0; u < BATCH; ++u) {
-        const int i = tid + (first + u) * THREADS;
+        const int i = first + u * THREADS;
         const int m = i / CHUNKS, c = i - m * CHUNKS;
-                raw[u] = (first + u < PER && m < M) ? ld_prev(reinterpret_cast<const uint4*>(A + (size_t)m * lda + c * 8)) : zero;
+        raw[u] = i < items ? ld_prev(reinterpret_cast<const uint4*>(A + (size_t)m * lda + c * 8)) : zero;
       }
     };
-    fetch(0);
+    fetch(tid);
+    if (rs < MP)
+      for (int c = tid; c < CHUNKS; c += THREADS) *reinterpret_cast<uint4*>(a_res + (size_t)rs * KA + c * 8) = zero;
     for (int m = warp; m < MP; m += WARPS) {
       float s = 0.f;
       if (m < M)
@@ -200,15 +222,15 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
     }
     __syncthreads();   // inv_s and the norm's weight are in shared memory
 #pragma unroll 1
-    for (int first = 0; first < PER; first += BATCH) {
-      if (first > 0) fetch(first);
+    for (int first = tid; first < items; first += BATCH * THREADS) {
+      if (first != tid) fetch(first);
 #pragma unroll
       for (int u = 0; u < BATCH; ++u) {
-        if (first + u >= PER) break;
-        const int i = tid + (first + u) * THREADS;
+        const int i = first + u * THREADS;
+        if (i >= items) break;
         const int m = i / CHUNKS, c = i - m * CHUNKS;
         uint4 out = zero;
-        if (m < M) {
+        {
           // two elements at a time: x * inv in 32-bit, rounded to a bfloat16 pair, times the weight pair
           // (a bfloat16 product rounded once: the same value as the 32-bit product rounded)
           const uint4 wraw = *reinterpret_cast<const uint4*>(nw_s + c * 8);
@@ -230,9 +252,11 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
   }
   // this thread's activation fragments: batch row mb*8 + g, k as for the weights
   constexpr bool STAGED = PRO != PLAIN;   // the block's activations are in shared memory
-  const bf16* a_frag = STAGED ? a_res + (size_t)g * KA + k_warp : A + (size_t)g * lda + k_warp;
-  const size_t a_mb = STAGED ? (size_t)8 * KA : (size_t)8 * lda;
-  int buf = 0;
+  const bf16* a_frag = A + (size_t)g * lda + k_warp;
+  const size_t a_mb = (size_t)8 * lda;
+  const bf16* a_row[MB];   // STAGED: where batch row mb * 8 + g lies (the row of zeros from rs on)
+#pragma unroll
+  for (int mb = 0; mb < MB; ++mb) a_row[mb] = a_res + (size_t)(mb * 8 + g < rs ? mb * 8 + g : rs) * KA + k_warp;
   for (; tile < n_tiles; tile += gridDim.x) {
     float acc[MB][4];
 #pragma unroll
@@ -249,7 +273,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
 #pragma unroll
         for (int mb = 0; mb < MB; ++mb) {
           uint4 a = zero;
-          if (STAGED) a = *reinterpret_cast<const uint4*>(a_frag + mb * a_mb + (chunk * CHUNK + u) * 32);
+          if (STAGED) a = *reinterpret_cast<const uint4*>(a_row[mb] + (chunk * CHUNK + u) * 32);
           else if (mb * 8 + g < M) a = ld_prev(reinterpret_cast<const uint4*>(a_frag + mb * a_mb + (chunk * CHUNK + u) * 32));
           mma16816(acc[mb], wa[u].x, wb[u].x, wa[u].y, wb[u].y, a.x, a.y);
           mma16816(acc[mb], wa[u].z, wb[u].z, wa[u].w, wb[u].w, a.z, a.w);
@@ -276,9 +300,8 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
         if (lane == 0) inv_s[warp + 8 * mb] = rsqrtf(sm / (float)K + eps);   // visible after the barrier below
       }
     }
-    // partial sums -> shared memory (two buffers, so one barrier per tile is enough)
-    float* red = red_base + buf * RED;
-    buf ^= 1;
+    // partial sums -> shared memory, once the tile before this one has been read from there
+    __syncthreads();
 #pragma unroll
     for (int mb = 0; mb < MB; ++mb) {
       red[(warp * ROWS + g) * (MP + 1) + mb * 8 + 2 * t] = acc[mb][0];
@@ -341,16 +364,22 @@ int launch3(const void* A, int lda, const void* W, void* C, int ldc, int M, int 
             cudaStream_t st) {
   constexpr bool NORM = PRO == NORMED;
   constexpr int MP = 8 * MB;
-  size_t smem = (size_t)2 * WARPS * ROWS * (MP + 1) * 4 + SS_STRIDE * 4;
-  if (NORM) smem += (size_t)MP * KA * 2 + (size_t)K * 2;
-  if (PRO == SCALED) smem += (size_t)MP * KA * 2;
-  if (smem > 110 * 1024) return DRYFT_ERR_UNSUPPORTED;
-  static size_t attr_bytes = 48 * 1024;  // per instantiation; raised by an eager launch before any capture
-  if (smem > attr_bytes) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_decode_kernel<MB, MODE, PRO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  const int rs = M < MP ? M : MP;                      // activation rows there are
+  const int staged = PRO == PLAIN ? 0 : (rs < MP ? rs + 1 : MP);   // and the row of zeros behind them
+  const size_t fixed = head_bytes<MB, PRO>() + SS_STRIDE * 4;
+  const size_t smem = fixed + (size_t)staged * KA * 2;
+  const size_t smem_max = fixed + (size_t)(PRO == PLAIN ? 0 : MP) * KA * 2;
+  if (smem + 1024 > SMEM_MOST) return DRYFT_ERR_UNSUPPORTED;
+  static bool attr_done = false;  // per instantiation; set by an eager launch before any capture
+  if (!attr_done) {
+    const size_t most = smem_max + 1024 > SMEM_MOST ? SMEM_MOST - 1024 : smem_max;
+    cudaError_t e = cudaFuncSetAttribute(gemm_decode_kernel<MB, MODE, PRO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(gemm_decode_kernel<MB, MODE, PRO>, cudaFuncAttributePreferredSharedMemoryCarveout, CARVEOUT_PCT);
     if (e != cudaSuccess) return (int)e;
-    attr_bytes = smem;
+    attr_done = true;
   }
+  const int blocks_per_sm = 2 * (smem + 1024) <= CARVEOUT_BYTES ? 2 : 1;
   // Persistent blocks, two per SM, each taking every grid-th tile.  What an SM can pull from memory is
   // bounded by the requests its blocks keep in flight, so the tiles are spread over all SMs as evenly as
   // they go: with the usual placement (block b beside block b + SMs) the SMs' totals differ by one tile.
@@ -359,10 +388,10 @@ int launch3(const void* A, int lda, const void* W, void* C, int ldc, int M, int 
     int dev = 0, sms = 0;
     cudaGetDevice(&dev);
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    max_blocks = 2 * (sms > 0 ? sms : 148);
+    max_blocks = sms > 0 ? sms : 148;
   }
   const int n_tiles = MODE == SILU ? (N + 7) / 8 : (N + ROWS - 1) / ROWS;
-  const unsigned blocks = (unsigned)(n_tiles < max_blocks ? n_tiles : max_blocks);
+  const unsigned blocks = (unsigned)(n_tiles < blocks_per_sm * max_blocks ? n_tiles : blocks_per_sm * max_blocks);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(blocks);
   cfg.blockDim = dim3(THREADS);
@@ -374,7 +403,7 @@ int launch3(const void* A, int lda, const void* W, void* C, int ldc, int M, int 
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_decode_kernel<MB, MODE, PRO>, (const bf16*)A, lda, (const bf16*)W, C, ldc, M,
-                                     N, norm_w, ss_in, ss_parts, eps, ss_out, next_w, (bf16*)xw_out);
+                                     N, norm_w, ss_in, ss_parts, eps, ss_out, next_w, (bf16*)xw_out, rs);
   if (e != cudaSuccess) return (int)e;
   return launch_status();
 }
