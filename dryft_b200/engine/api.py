@@ -45,7 +45,7 @@ class EngineOptions:
     page_size: int = 64
     cuda_graphs: bool = True
     device: str = "cuda:0"
-    small_m_max: int = 8                   # rows up to which decode products stream weights through registers (mma.sync)
+    small_m_max: int = 16                   # rows up to which decode products stream weights through registers (mma.sync)
     stream_m_max: int = 0                  # rows up to which they stream them by TMA into tcgen05.mma above that (0: cuBLAS,
                                            # which is faster today: profiles/gemm_stream_microbench.md)
     fuse_decode: bool = True               # fold norms, adds and SiLU*mul into the decode products

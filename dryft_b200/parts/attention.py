@@ -116,8 +116,6 @@ class Attention:
             # eight such clusters some wait for a whole GPC's worth of SMs (batch 2 at 2,063 keys: 20.8 us a
             # layer with 16 clusters of 8 against 12.9 us with 16 clusters of 4)
             by_cluster = 4
-        if pages <= 16 and 4 * n_rows * self.n_kv > self.rt.sm_count:
-            by_cluster = 1   # up to 1,024 keys a block's eight warps are enough unless most SMs would idle
         by_memory = min(32, (max(1, max_kv) + 1023) // 1024)
         if by_memory > self.CLUSTER_SPLITS:
             # also within one block per SM where the batch allows it (batch 1 at 32,768 keys: 18 splits, not 32:
@@ -128,7 +126,7 @@ class Attention:
     def can_fuse(self, n_rows: int, norm) -> bool:
         """Few rows, bfloat16 everywhere, widths the weight-streaming product takes."""
         rt = self.rt
-        return (rt.fuse_decode and rt.is_bf16 and fusable_rows(n_rows, self.hidden, rt) and fusable_rows(n_rows, self.q_dim, rt)
+        return (rt.fuse_decode and rt.is_bf16 and fusable_rows(n_rows, self.hidden, rt, normed=True) and fusable_rows(n_rows, self.q_dim, rt)
                 and fused_rms(norm) is not None and self.w_qkv.dtype == torch.bfloat16 and self.w_o.dtype == torch.bfloat16)
 
     weighted_ahead = True   # forward_normed takes ``xw`` / ``next_norm`` and returns the weighted stream too

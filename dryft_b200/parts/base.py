@@ -52,7 +52,7 @@ class Runtime:
     device: torch.device
     page_size: int = 64
     sm_count: int = 148
-    small_m_max: int = 8         # decode rows up to which weights stream through registers into mma.sync (csrc/gemm_decode.cu)
+    small_m_max: int = 16         # decode rows up to which weights stream through registers into mma.sync (csrc/gemm_decode.cu)
     stream_m_max: int = 0        # decode rows up to which the tcgen05 weight-streaming product runs above that (0: the library's)
     ffn_chunk_rows: int = 16384  # rows of the feed-forward processed at once (bounds [rows, 2I])
     fuse_decode: bool = True     # few rows: fold norms, residual adds and SiLU*mul into the products

@@ -71,7 +71,7 @@ class LMHead:
 
     def can_fuse(self, n_rows: int, norm) -> bool:
         rt = self.rt
-        return (rt.fuse_decode and rt.is_bf16 and fusable_rows(n_rows, self.weight.shape[1], rt)
+        return (rt.fuse_decode and rt.is_bf16 and fusable_rows(n_rows, self.weight.shape[1], rt, normed=True)
                 and fused_rms(norm) is not None and self.weight.dtype == torch.bfloat16)
 
     def forward_normed(self, x: torch.Tensor, ss, ss_parts: int, norm, xw=None) -> torch.Tensor:

@@ -36,7 +36,7 @@ class SwiGLU:
 
     def can_fuse(self, n_rows: int, norm) -> bool:
         rt = self.rt
-        return (rt.fuse_decode and rt.is_bf16 and fusable_rows(n_rows, self.hidden, rt) and fusable_rows(n_rows, self.inter, rt)
+        return (rt.fuse_decode and rt.is_bf16 and fusable_rows(n_rows, self.hidden, rt, normed=True) and fusable_rows(n_rows, self.inter, rt)
                 and fused_rms(norm) is not None and self.w_gate_up.dtype == torch.bfloat16 and self.w_down.dtype == torch.bfloat16)
 
     weighted_ahead = True   # forward_normed takes ``xw`` / ``next_norm`` and returns the weighted stream too

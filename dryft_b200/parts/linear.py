@@ -41,7 +41,7 @@ def linear(x: torch.Tensor, w: torch.Tensor, rt: Runtime, out_dtype: Optional[to
         return out if out_dtype == torch.float32 else out.to(out_dtype)
     if w.dtype != torch.bfloat16:
         raise ValueError(f"linear: weight dtype {w.dtype} is not supported")
-    if m <= min(rt.small_m_max, K.SMALL_M_LIMIT) and k % 16 == 0:
+    if K.fused_rows_supported(m, k, rt.small_m_max, 0, normed=True):   # above 8 rows: the narrow widths only
         out = torch.empty((m, n), dtype=out_dtype, device=x.device)
         K.gemm_small_m(x, w, out)
         return out
@@ -54,9 +54,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, rt: Runtime, out_dtype: Optional[to
     return torch.mm(x, w.t(), out_dtype=out_dtype)
 
 
-def fusable_rows(n_rows: int, k: int, rt: Runtime) -> bool:
-    """Whether the fused decode products take ``n_rows`` rows over ``k`` inputs."""
-    return K.fused_rows_supported(n_rows, k, rt.small_m_max, rt.stream_m_max if rt.tcgen05 else 0)
+def fusable_rows(n_rows: int, k: int, rt: Runtime, normed: bool = False) -> bool:
+    """Whether the fused decode products take ``n_rows`` rows over ``k`` inputs (``normed``: with a norm on the way in)."""
+    return K.fused_rows_supported(n_rows, k, rt.small_m_max, rt.stream_m_max if rt.tcgen05 else 0, normed)
 
 
 def weighted_for(next_norm, width: int, k_in: int, rt: Runtime, n_rows: int = 1) -> bool:

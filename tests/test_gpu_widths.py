@@ -97,6 +97,23 @@ def step(eng, slots, tokens, want):
         return eng.stepper.step(slots, tokens, want)
 
 
+def same_choices(dirs, name, dtype, prompt, one, other, what):
+    """Two runs of one sequence in different company.  32-bit: the same tokens.  bfloat16: the company decides
+    which kernels run (library products above 16 rows, register-streaming ones below), whose sums round
+    differently, so the runs agree up to the first position where the plain model's logits of the two choices
+    lie closer together than bfloat16 rounding moves them; from there each run is checked on its own."""
+    if list(one) == list(other):
+        return
+    assert dtype == torch.bfloat16, what
+    i = next(j for j in range(min(len(one), len(other))) if one[j] != other[j])
+    seq_tokens = list(prompt) + list(one[:i])
+    lg = plain_logits(dirs, name, torch.float32, seq_tokens)[-1]
+    pb = plain_logits(dirs, name, torch.bfloat16, seq_tokens)[-1]
+    allowed = 2.0 * float((pb - lg).abs().max()) + 1e-3 * float(lg.abs().max())
+    gap = abs(float(lg[one[i]] - lg[other[i]]))
+    assert gap <= allowed, f"{what}: token {i} is {one[i]} / {other[i]}, plain logits {gap:.3g} apart (allowed {allowed:.3g})"
+
+
 def check_generated(dirs, name, dtype, prompt, ours, what, temperature=0.0, top_k=0, seed=0, seq=0):
     """Teacher-forced check of generated tokens (``agent/verify.py:100-109``): one plain pass over the prompt and
     our tokens.  32-bit: every token is the plain model's choice (argmax, or the same draw).  bfloat16, greedy:
@@ -242,7 +259,7 @@ def test_wide_generation_across_batch_bucket_edges_with_stop_tokens(dirs, dtype,
         n = next((i + 1 for i, t in enumerate(col) if t in stops), len(col))
         assert all(t == -1 for t in col[n:]) and all(t >= 0 for t in col[:n]), f"sequence {b}: {col}"
         # a sequence's tokens do not depend on who else is still in the batch: equal to the free run's
-        assert col[:n] == [s[b] for s in free][:n], f"sequence {b} changed when others left"
+        same_choices(dirs, "wide", dtype, p, col[:n], [s[b] for s in free][:n], f"sequence {b} changed when others left")
         check_generated(dirs, "wide", dtype, p, col[:n], f"wide stops, sequence {b}", seq=b, **kw)
     many = eng.generate_many(ps, 14, stop_token_ids=stops, **kw)
     for b in range(len(ps)):

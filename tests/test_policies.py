@@ -33,3 +33,19 @@ def test_decode_splits_of_a_long_single_sequence():
     assert _splits(4096, 2) == 4        # 16 clusters: of four blocks, not of eight
     assert _splits(4096, 1) == 8
     assert _splits(512, 64) == 1
+
+
+def test_products_of_nine_to_sixteen_rows_stay_under_the_shared_memory_cut():
+    from dryft_b200.ops import kernels as K
+    # up to 8 rows: always the register-streaming product, whatever the width
+    assert K.fused_rows_supported(8, 5120, 16, 0, normed=True)
+    assert K.fused_rows_supported(1, 8192, 16, 0, normed=True)
+    # 9 to 16 rows with the norm on the way in: only widths whose 16 staged rows leave a block under 100 KB
+    assert K.small_m_staged_bytes(16, 2560) == 8704 + 256 + 16 * 2592 * 2 + 1024
+    assert K.fused_rows_supported(16, 2560, 16, 0, normed=True)
+    assert not K.fused_rows_supported(10, 4096, 16, 0, normed=True)   # ten rows would fit, sixteen do not
+    assert not K.fused_rows_supported(9, 5120, 16, 0, normed=True)
+    # plain activations are not staged: no such limit
+    assert K.fused_rows_supported(16, 25600, 16, 0)
+    # small_m_max still bounds it
+    assert not K.fused_rows_supported(9, 2560, 8, 0, normed=True)
