@@ -10,15 +10,17 @@
 //   norm (rmsnorm.py:34), SiLU*mul epilogue (kernels/silu_mul.py:29-32; weights.py:98-100).
 //
 // A block of 8 warps takes 16 rows of W at a time; blocks are persistent, two per SM (one where the
-// staged activations are too large for two), each walking over every grid-th tile.  The warps split K into 8 equal ranges.  A warp requests its whole
-// share of the tile's 16 rows at once — K/128 16-byte loads per thread that bypass L1, all in flight
-// together — then feeds them to mma.sync.m16n8k16 with W as the 16 x 16 operand and 8 batch rows as
-// the 16 x 8 operand (the k index permuted identically in both operands, so that a thread's fragment
-// is one contiguous 16-byte piece).  While a warp consumes, the other fifteen on the SM have their
-// requests in flight.  With the norm prologue the normalised activations are made once per block and
-// stay in shared memory (the M rows there are and one row of zeros for the rest of the operand);
-// otherwise they are read through L2.  The 8 partial sums are added in warp order through shared
-// memory: a row's result depends neither on the other rows nor on M.
+// staged activations are too large for two), each walking over every grid-th tile.  The warps split K
+// into 8 equal ranges.  A thread keeps a ring of up to ten 32-wide k steps of its two weight rows in
+// registers -- 16-byte loads that bypass L1, all in flight together -- and feeds them to
+// mma.sync.m16n8k16 with W as the 16 x 16 operand and 8 batch rows as the 16 x 8 operand (the k index
+// permuted identically in both operands, so that a thread's fragment is one contiguous 16-byte piece);
+// the registers of a step just multiplied take the step a ring's length further on, of this tile or of
+// the block's next one, so a warp's requests never drain.  With the norm prologue the normalised
+// activations are made once per block and stay in shared memory (the M rows there are and one row of
+// zeros for the rest of the operand); otherwise they are read through L2, a few steps ahead.  The 8
+// partial sums are added in warp order through shared memory: a row's result depends neither on the
+// other rows nor on M.
 //
 // The norm can also be split between two launches, which takes it off the consumer's critical path: a
 // residual product that knows the next norm's weight w leaves, beside the new stream x, the weighted
@@ -44,8 +46,28 @@ constexpr int WARPS = 8;
 constexpr int THREADS = WARPS * 32;
 constexpr int ROWS = 16;
 constexpr int SPW = K / 32 / WARPS;           // 32-wide k steps per warp
-constexpr int CHUNK = SPW <= 10 ? SPW : 10;     // steps a warp requests together (the last chunk may be shorter)
-constexpr int N_CHUNKS = (SPW + CHUNK - 1) / CHUNK;
+// A thread keeps CHUNK steps of its two weight rows in registers, as a ring: the registers of the step just
+// multiplied take the step CHUNK further on, of this tile or of the block's next one, so that a warp's
+// requests never drain.  The ring's slot of a step is (step mod CHUNK) in every tile, so a tile is walked in
+// SPWP steps, a multiple of CHUNK; the steps from SPW on are empty.  CHUNK is the ring of 6 to 10 steps that
+// keeps most steps in flight after those empty ones.
+__host__ __device__ constexpr int pick_chunk(int most) {
+  if (SPW <= most) return SPW;
+  int best = most, best_score = 0;
+  for (int c = 6; c <= most; ++c) {
+    const int score = SPW * c * 64 / ((SPW + c - 1) / c * c);
+    if (score > best_score) { best = c; best_score = score; }   // ties: the shorter ring
+  }
+  return best;
+}
+// plain activations come from L2 a few steps ahead, in a ring of registers of their own whose length divides
+// the weights' ring; 16 rows of them take twice the registers, so the weights' ring is at most 8 steps there
+__host__ __device__ constexpr int pick_ahead(int chunk, int most) {
+  int d = 1;
+  for (int c = 1; c <= most; ++c)
+    if (chunk % c == 0) d = c;
+  return d;
+}
 constexpr int SS_STRIDE = 64;
 constexpr int KA = K + ((64 - (K * 2) % 128 + 128) % 128) / 2;  // resident row stride: bytes = 64 mod 128
 
@@ -95,6 +117,8 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
   constexpr bool NORM = PRO == NORMED;
   constexpr int MP = 8 * MB;
   constexpr int RED = WARPS * ROWS * (MP + 1);
+  constexpr int CHUNK = pick_chunk(MB == 2 && PRO == PLAIN ? 8 : 10);
+  constexpr int SPWP = (SPW + CHUNK - 1) / CHUNK * CHUNK;
   extern __shared__ __align__(16) unsigned char smem[];
   // [WARPS][ROWS][MP + 1] partial sums (the norm's weight lies in the same bytes until the first tile is
   // reduced), 64 floats of inv, then the resident activations: the rs = min(M, MP) rows there are, and one
@@ -122,20 +146,15 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
     w0 = ok0 ? W + (size_t)r0 * K + k_warp : nullptr;
     w1 = ok1 ? W + (size_t)r1 * K + k_warp : nullptr;
   };
-  auto request = [&](const bf16* w0, const bf16* w1, const int chunk) {
-#pragma unroll
-    for (int u = 0; u < CHUNK; ++u) {
-      if (chunk * CHUNK + u < SPW) {  // folds away: both are constants once unrolled
-        wa[u] = w0 ? ld_stream(w0 + (chunk * CHUNK + u) * 32) : zero;
-        wb[u] = w1 ? ld_stream(w1 + (chunk * CHUNK + u) * 32) : zero;
-      }
-    }
-  };
   int tile = blockIdx.x;
   const bf16 *w0 = nullptr, *w1 = nullptr;
   if (tile < n_tiles) {
     rows_of(tile, w0, w1);
-    request(w0, w1, 0);  // weights depend on no earlier launch
+#pragma unroll
+    for (int u = 0; u < CHUNK; ++u) {   // the first tile's first steps: weights depend on no earlier launch
+      wa[u] = w0 ? ld_stream(w0 + u * 32) : zero;
+      wb[u] = w1 ? ld_stream(w1 + u * 32) : zero;
+    }
   }
 
   bf16* nw_s = reinterpret_cast<bf16*>(smem);   // the norm's weight as bfloat16 (its values are bfloat16 values held in 32-bit)
@@ -257,35 +276,58 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
   const bf16* a_row[MB];   // STAGED: where batch row mb * 8 + g lies (the row of zeros from rs on)
 #pragma unroll
   for (int mb = 0; mb < MB; ++mb) a_row[mb] = a_res + (size_t)(mb * 8 + g < rs ? mb * 8 + g : rs) * KA + k_warp;
+  // plain activations come from L2 AD steps ahead, in a ring of registers of their own
+  constexpr int AD = STAGED ? 1 : pick_ahead(CHUNK, MB == 1 ? 5 : 4);
+  uint4 ar[MB][AD];
+  auto plain_a = [&](int mb, int step) {
+    return mb * 8 + g < M ? ld_prev(reinterpret_cast<const uint4*>(a_frag + mb * a_mb + step * 32)) : zero;
+  };
+  if (!STAGED && tile < n_tiles) {
+#pragma unroll
+    for (int mb = 0; mb < MB; ++mb)
+#pragma unroll
+      for (int u = 0; u < AD; ++u) ar[mb][u] = plain_a(mb, u);
+  }
   for (; tile < n_tiles; tile += gridDim.x) {
     float acc[MB][4];
 #pragma unroll
     for (int mb = 0; mb < MB; ++mb)
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[mb][i] = 0.f;
+    const int next = tile + gridDim.x;
+    const bool has_next = next < n_tiles;
+    const bf16 *nw0 = nullptr, *nw1 = nullptr;
+    if (has_next) rows_of(next, nw0, nw1);
 
 #pragma unroll
-    for (int chunk = 0; chunk < N_CHUNKS; ++chunk) {
-      if (chunk > 0) request(w0, w1, chunk);
+    for (int s = 0; s < SPWP; ++s) {
+      const int u = s % CHUNK;
 #pragma unroll
-      for (int u = 0; u < CHUNK; ++u) {
-        if (chunk * CHUNK + u >= SPW) continue;
-#pragma unroll
-        for (int mb = 0; mb < MB; ++mb) {
-          uint4 a = zero;
-          if (STAGED) a = *reinterpret_cast<const uint4*>(a_row[mb] + (chunk * CHUNK + u) * 32);
-          else if (mb * 8 + g < M) a = ld_prev(reinterpret_cast<const uint4*>(a_frag + mb * a_mb + (chunk * CHUNK + u) * 32));
+      for (int mb = 0; mb < MB; ++mb) {
+        if (s < SPW) {
+          const uint4 a = STAGED ? *reinterpret_cast<const uint4*>(a_row[mb] + s * 32) : ar[mb][s % AD];
           mma16816(acc[mb], wa[u].x, wb[u].x, wa[u].y, wb[u].y, a.x, a.y);
           mma16816(acc[mb], wa[u].z, wb[u].z, wa[u].w, wb[u].w, a.z, a.w);
         }
+        if (!STAGED) {   // the slot takes the step AD further on; the activations are the same for every tile
+          const int ta = s + AD < SPWP ? s + AD : s + AD - SPWP;
+          if (ta < SPW && (s + AD < SPWP || has_next)) ar[mb][s % AD] = plain_a(mb, ta);
+        }
+      }
+      // these registers take the step CHUNK further on: of this tile, or of the block's next one, whose
+      // first weights thus fly while this tile is reduced and written
+      if (s + CHUNK < SPWP) {
+        if (s + CHUNK < SPW) {
+          wa[u] = w0 ? ld_stream(w0 + (s + CHUNK) * 32) : zero;
+          wb[u] = w1 ? ld_stream(w1 + (s + CHUNK) * 32) : zero;
+        }
+      } else if (has_next && s + CHUNK - SPWP < SPW) {
+        wa[u] = nw0 ? ld_stream(nw0 + (s + CHUNK - SPWP) * 32) : zero;
+        wb[u] = nw1 ? ld_stream(nw1 + (s + CHUNK - SPWP) * 32) : zero;
       }
     }
-    // the next tile's first weights fly while this tile is reduced and written
-    const int next = tile + gridDim.x;
-    if (next < n_tiles) {
-      rows_of(next, w0, w1);
-      request(w0, w1, 0);
-    }
+    w0 = nw0;
+    w1 = nw1;
 
     if (PRO == SCALED && !inv_done) {
       inv_done = true;

@@ -58,7 +58,7 @@ def attn_prefill(token_counts=(2048, 8192)) -> None:
     K.check_error_flags()
 
 
-def decode_chain(layers: int = 36, small_rows=(1, 8), stream_rows=(16, 32, 64)) -> None:
+def decode_chain(layers: int = 36, small_rows=(1, 8, 16), stream_rows=(32, 64)) -> None:
     hidden, q_dim, inter = 2560, 4096, 9728
     w_qkv = (torch.randn(layers, 6144, hidden, device=DEV) * 0.02).to(BF)
     w_o = (torch.randn(layers, hidden, q_dim, device=DEV) * 0.02).to(BF)
