@@ -8,9 +8,11 @@
 // Grid (rows, kv heads, splits); a row is one sequence's new token.  Every block rebuilds the row's
 // GROUP rotated queries (cheap, and it saves a launch and a round trip through memory); the one block
 // whose page range holds the token's own position also makes the new key and value and writes them
-// into the cache before anyone in the block reads that page.  The GROUP query heads of the token form
-// the (zero-padded) 16-row operand of mma.sync.m16n8k16, so Q K^T and P V run on the tensor cores as
-// in the prefill kernel (csrc/attn_prefill.cu), with the heads where that kernel has query tokens.
+// into the cache before anyone in the block reads that page.  Both products run on the tensor cores
+// (mma.sync.m16n8k16) with a slice's 16 keys as the 16-row operand and the token's GROUP query heads as
+// the 8 columns (two column tiles above 8 heads): S^T = K Q^T, then O^T = V^T P^T with P transposed in
+// registers (movmatrix).  A group of four heads fills half of that operand; as the rows of a 16-row
+// operand it would fill a quarter, at twice the products, exponentials and accumulators.
 // Inside a block each warp walks over 16-key slices of its own (no block-wide barrier in the loop):
 // it requests the slice's K and V rows with cp.async into its own ring of shared-memory buffers, the
 // next slice in flight while one is used, the first requests going out before the queries are rebuilt (the
@@ -39,11 +41,12 @@ constexpr int SLICE = 16;                   // keys a warp handles at a time
 constexpr int SPP = PAGE / SLICE;           // slices per page
 constexpr int KS = D + 8;                   // padded row (elements): conflict-free ldmatrix
 constexpr int KSTEPS = D / 16;
-constexpr int DT = D / 8;
+constexpr int MT = D / 16;                  // 16-wide tiles of the head size
+constexpr int NT = (G + 7) / 8;             // 8-wide tiles of the query heads
 static_assert(D % 16 == 0 && D <= 256, "head size 16..256 in steps of 16");
 static_assert(G >= 1 && G <= 16, "1..16 query heads per kv head");
 static_assert(PAGE % SLICE == 0, "page size must be a multiple of 16");
-// shared memory: Q [16][KS] bf16 and the new token's K and V rows, then per warp STAGES stages of
+// shared memory: Q [8 or 16][KS] bf16 (rows from GROUP on zero) and the new token's K and V rows, then per warp STAGES stages of
 // (K slice, V slice) [16][KS] bf16 each.
 // The combine buffers (m, l: [NWARP][16]; acc: [NWARP][G][D] floats) overlay the stages at the end.
 // The block's shape is a template: NWARP warps with STAGES slices staged per warp (STAGES - 1 in flight
@@ -51,7 +54,8 @@ static_assert(PAGE % SLICE == 0, "page size must be a multiple of 16");
 // are walked by many warps.  Many pairs: narrow blocks with deeper rings, several per SM, so that no SM
 // waits on the one block it holds and the grid is not cut into a few coarse waves.
 constexpr int PT_CACHE = 64;                // page numbers of a block kept in shared memory (more are read from global)
-constexpr size_t Q_BYTES = (size_t)(16 + 2) * KS * 2;      // 16 query rows, then the new key and the new value
+constexpr int Q_ROWS = (G + 7) / 8 * 8;                     // the query heads, padded with zero rows to whole column tiles
+constexpr size_t Q_BYTES = (size_t)(Q_ROWS + 2) * KS * 2;  // then the new key and the new value
 template <int NWARP, int STAGES> struct Shape {
   static constexpr int THREADS = NWARP * 32;
   static constexpr size_t WARP_STAGE_BYTES = (size_t)STAGES * 2 * SLICE * KS * 2;
@@ -69,6 +73,16 @@ template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile(
 __device__ __forceinline__ void ldsm_x4(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
   unsigned s = (unsigned)__cvta_generic_to_shared(p);
   asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(s));
+}
+__device__ __forceinline__ void ldsm_x2(unsigned& r0, unsigned& r1, const void* p) {
+  unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0,%1}, [%2];" : "=r"(r0), "=r"(r1) : "r"(s));
+}
+// an 8 x 8 block of 16-bit values held as an mma fragment (row lane / 4, columns 2 (lane mod 4) and + 1), transposed
+__device__ __forceinline__ unsigned movmatrix_t(unsigned v) {
+  unsigned r;
+  asm volatile("movmatrix.sync.aligned.m8n8.trans.b16 %0, %1;" : "=r"(r) : "r"(v));
+  return r;
 }
 __device__ __forceinline__ void ldsm_x4_t(unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3, const void* p) {
   unsigned s = (unsigned)__cvta_generic_to_shared(p);
@@ -190,7 +204,7 @@ __global__ void __launch_bounds__(NWARP * 32) attn_decode_kernel(const Params p)
   constexpr int THREADS = Shape<NWARP, STAGES>::THREADS;
   constexpr size_t WARP_STAGE_BYTES = Shape<NWARP, STAGES>::WARP_STAGE_BYTES;
   extern __shared__ __align__(16) unsigned char smem[];
-  bf16* qs = reinterpret_cast<bf16*>(smem);                        // [16][KS], rows >= G zero
+  bf16* qs = reinterpret_cast<bf16*>(smem);                        // [Q_ROWS][KS], rows >= G zero
   unsigned char* pipe = smem + Q_BYTES;
   __shared__ int is_last;
 
@@ -272,9 +286,9 @@ __global__ void __launch_bounds__(NWARP * 32) attn_decode_kernel(const Params p)
   }
 
   // ---- the row's queries; and, in the block that owns the last page, the new key and value ----
-  bf16* new_k = qs + 16 * KS;
+  bf16* new_k = qs + Q_ROWS * KS;
   bf16* new_v = new_k + KS;
-  for (int i = tid; i < (16 - G) * (D / 8); i += THREADS)  // zero the padding rows of Q
+  for (int i = tid; i < (Q_ROWS - G) * (D / 8); i += THREADS)  // zero the padding rows of Q
     *reinterpret_cast<uint4*>(qs + (G + i / (D / 8)) * KS + (i % (D / 8)) * 8) = make_uint4(0, 0, 0, 0);
   const bool owns_new = p.write_kv && last_page >= pg_begin && last_page < pg_end;
   const int n_items = G + (owns_new ? 2 : 0);
@@ -298,13 +312,30 @@ __global__ void __launch_bounds__(NWARP * 32) attn_decode_kernel(const Params p)
   __syncthreads();  // queries (and the new key and value) are in shared memory
 
   // ---- each warp walks its own 16-key slices of the block's pages ----
-  float o_acc[DT][4];
+  // The slice's 16 keys are the 16-row operand and the query heads the 8 columns (NT column tiles for more
+  // than 8 heads): S^T = K Q^T and O^T = V^T P^T.  With the heads as the 16 rows, a group of four would
+  // fill a quarter of the operand; this way it fills half, with half the products, exponentials and
+  // accumulators.  A thread holds, of every tile, keys (or head dims) g and g + 8 for heads 2t and 2t + 1.
+  float o_acc[NT][MT][4];
 #pragma unroll
-  for (int j = 0; j < DT; ++j)
+  for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) o_acc[j][i] = 0.f;
-  float m_run[2] = {-INFINITY, -INFINITY};  // rows g and g+8 (heads), in log2 units
-  float l_run[2] = {0.f, 0.f};              // this thread's share of the row sums
+    for (int j = 0; j < MT; ++j)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o_acc[nt][j][i] = 0.f;
+  float m_run[NT][2], l_run[NT][2];   // heads nt*8 + 2t and + 1: running maximum (log2 units), this thread's share of the sum
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt) { m_run[nt][0] = m_run[nt][1] = -INFINITY; l_run[nt][0] = l_run[nt][1] = 0.f; }
+  // the queries' operand fragments are the same for every slice: read from shared memory once where they are few
+  constexpr bool Q_IN_REGS = NT * KSTEPS * 2 <= 32;
+  unsigned qb[Q_IN_REGS ? NT : 1][Q_IN_REGS ? KSTEPS : 1][2];
+  const bf16* q_lane = qs + (lane & 7) * KS + ((lane >> 3) & 1) * 8;   // head (lane mod 8) of a column tile, low or high 8 of a k step
+  if (Q_IN_REGS) {
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int kk = 0; kk < KSTEPS; ++kk) ldsm_x2(qb[nt][kk][0], qb[nt][kk][1], q_lane + nt * 8 * KS + kk * 16);
+  }
   const float scale_log2 = p.scale * 1.4426950408889634f;
 
   int it = 0;
@@ -331,83 +362,77 @@ __global__ void __launch_bounds__(NWARP * 32) attn_decode_kernel(const Params p)
       __syncwarp();
     }
 
-    // S = Q K^T: 16 (heads, padded) x 16 keys
-    // the k steps go round NCH accumulators per key half: chains of dependent products NCH times shorter
-    constexpr int NCH = KSTEPS >= 2 ? 2 : 1;   // four chains measured no better than two
-    float sp[NCH][2][4];
+    // S^T = K Q^T: 16 keys x 8 heads per column tile; the k steps go round two accumulators (chains of
+    // dependent products half as long)
+    constexpr int NCH = KSTEPS >= 2 ? 2 : 1;
+    float sp[NCH][NT][4];
 #pragma unroll
     for (int c = 0; c < NCH; ++c)
 #pragma unroll
-      for (int j = 0; j < 2; ++j)
+      for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) sp[c][j][i] = 0.f;
+        for (int i = 0; i < 4; ++i) sp[c][nt][i] = 0.f;
 #pragma unroll
     for (int kk = 0; kk < KSTEPS; ++kk) {
-      unsigned a0, a1, a2, a3, b0, b1, b2, b3;
-      ldsm_x4(a0, a1, a2, a3, qs + (lane & 15) * KS + kk * 16 + (lane >> 4) * 8);
-      ldsm_x4(b0, b1, b2, b3, kst + ((lane & 7) + (lane >> 4) * 8) * KS + kk * 16 + ((lane >> 3) & 1) * 8);
-      mma16816(sp[kk % NCH][0], a0, a1, a2, a3, b0, b1);
-      mma16816(sp[kk % NCH][1], a0, a1, a2, a3, b2, b3);
-    }
-    float s[2][4];
+      unsigned a0, a1, a2, a3;
+      ldsm_x4(a0, a1, a2, a3, kst + (lane & 15) * KS + kk * 16 + (lane >> 4) * 8);
 #pragma unroll
-    for (int j = 0; j < 2; ++j)
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float t = sp[0][j][i];
-#pragma unroll
-        for (int c = 1; c < NCH; ++c) t += sp[c][j][i];
-        s[j][i] = t;
+      for (int nt = 0; nt < NT; ++nt) {
+        unsigned b0, b1;
+        if (Q_IN_REGS) { b0 = qb[nt][kk][0]; b1 = qb[nt][kk][1]; }
+        else ldsm_x2(b0, b1, q_lane + nt * 8 * KS + kk * 16);
+        mma16816(sp[kk % NCH][nt], a0, a1, a2, a3, b0, b1);
       }
+    }
     // mask, online softmax (log2 domain); every slice visited holds at least one visible key
     const int key0 = sl * SLICE;
-    float mx0 = -INFINITY, mx1 = -INFINITY;
+    const bool in0 = key0 + g >= kv_lo && key0 + g < kv_hi, in1 = key0 + g + 8 >= kv_lo && key0 + g + 8 < kv_hi;
+    unsigned pb[NT][2];
 #pragma unroll
-    for (int j = 0; j < 2; ++j)
+    for (int nt = 0; nt < NT; ++nt) {
+      float v[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int kp = key0 + j * 8 + 2 * t + (i & 1);
-        const float v = (kp >= kv_lo && kp < kv_hi) ? s[j][i] * scale_log2 : -INFINITY;
-        s[j][i] = v;
-        if (i < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+        float t2 = sp[0][nt][i];
+#pragma unroll
+        for (int c = 1; c < NCH; ++c) t2 += sp[c][nt][i];
+        v[i] = ((i < 2) ? in0 : in1) ? t2 * scale_log2 : -INFINITY;
       }
-    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
-    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
-    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
-    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-    const float mn0 = fmaxf(m_run[0], mx0), mn1 = fmaxf(m_run[1], mx1);
-    const float mu0 = (mn0 == -INFINITY) ? 0.f : mn0, mu1 = (mn1 == -INFINITY) ? 0.f : mn1;
-    const float al0 = exp2f(m_run[0] - mu0), al1 = exp2f(m_run[1] - mu1);
-    m_run[0] = mn0;
-    m_run[1] = mn1;
-    float sum0 = 0.f, sum1 = 0.f;
+      float mx0 = fmaxf(v[0], v[2]), mx1 = fmaxf(v[1], v[3]);   // heads 2t and 2t + 1 over this thread's two keys
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
-      s[j][0] = exp2f(s[j][0] - mu0);
-      s[j][1] = exp2f(s[j][1] - mu0);
-      s[j][2] = exp2f(s[j][2] - mu1);
-      s[j][3] = exp2f(s[j][3] - mu1);
-      sum0 += s[j][0] + s[j][1];
-      sum1 += s[j][2] + s[j][3];
+      for (int o = 4; o < 32; o <<= 1) {                          // ... and over the eight threads that hold the other keys
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, o));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, o));
+      }
+      const float mn0 = fmaxf(m_run[nt][0], mx0), mn1 = fmaxf(m_run[nt][1], mx1);
+      const float mu0 = (mn0 == -INFINITY) ? 0.f : mn0, mu1 = (mn1 == -INFINITY) ? 0.f : mn1;
+      const float al0 = exp2f(m_run[nt][0] - mu0), al1 = exp2f(m_run[nt][1] - mu1);
+      m_run[nt][0] = mn0;
+      m_run[nt][1] = mn1;
+      v[0] = exp2f(v[0] - mu0);
+      v[1] = exp2f(v[1] - mu1);
+      v[2] = exp2f(v[2] - mu0);
+      v[3] = exp2f(v[3] - mu1);
+      l_run[nt][0] = l_run[nt][0] * al0 + (v[0] + v[2]);
+      l_run[nt][1] = l_run[nt][1] * al1 + (v[1] + v[3]);
+#pragma unroll
+      for (int j = 0; j < MT; ++j) {
+        o_acc[nt][j][0] *= al0;
+        o_acc[nt][j][1] *= al1;
+        o_acc[nt][j][2] *= al0;
+        o_acc[nt][j][3] *= al1;
+      }
+      // P (bfloat16) as the second product's k x n operand: the 8 x 8 blocks (keys x heads) transposed in registers
+      pb[nt][0] = movmatrix_t(pack_bf16(v[0], v[1]));
+      pb[nt][1] = movmatrix_t(pack_bf16(v[2], v[3]));
     }
-    l_run[0] = l_run[0] * al0 + sum0;
-    l_run[1] = l_run[1] * al1 + sum1;
+    // O^T += V^T P^T (one k16 step: the slice's 16 keys), 16 head dims a product
 #pragma unroll
-    for (int j = 0; j < DT; ++j) {
-      o_acc[j][0] *= al0;
-      o_acc[j][1] *= al0;
-      o_acc[j][2] *= al1;
-      o_acc[j][3] *= al1;
-    }
-    // O += P V (one k16 step: the slice's 16 keys)
-    const unsigned pa0 = pack_bf16(s[0][0], s[0][1]), pa1 = pack_bf16(s[0][2], s[0][3]);
-    const unsigned pa2 = pack_bf16(s[1][0], s[1][1]), pa3 = pack_bf16(s[1][2], s[1][3]);
+    for (int j = 0; j < MT; ++j) {
+      unsigned a0, a1, a2, a3;
+      ldsm_x4_t(a0, a1, a2, a3, vst + ((lane & 7) + (lane >> 4) * 8) * KS + j * 16 + ((lane >> 3) & 1) * 8);
 #pragma unroll
-    for (int j = 0; j < DT; j += 2) {
-      unsigned b0, b1, b2, b3;
-      ldsm_x4_t(b0, b1, b2, b3, vst + ((lane & 7) + ((lane >> 3) & 1) * 8) * KS + j * 8 + (lane >> 4) * 8);
-      mma16816(o_acc[j], pa0, pa1, pa2, pa3, b0, b1);
-      mma16816(o_acc[j + 1], pa0, pa1, pa2, pa3, b2, b3);
+      for (int nt = 0; nt < NT; ++nt) mma16816(o_acc[nt][j], a0, a1, a2, a3, pb[nt][0], pb[nt][1]);
     }
     __syncwarp();  // the stage may be refilled by the request two iterations on
   }
@@ -418,20 +443,25 @@ __global__ void __launch_bounds__(NWARP * 32) attn_decode_kernel(const Params p)
   float* wm = reinterpret_cast<float*>(pipe);          // [NWARP][16]
   float* wl = wm + NWARP * 16;                         // [NWARP][16]
   float* wacc = wl + NWARP * 16;                       // [NWARP][G][D]
-  float l0 = l_run[0], l1 = l_run[1];
-  l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
-  l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-  l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
-  l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-  if (t == 0) {
-    wm[warp * 16 + g] = m_run[0]; wl[warp * 16 + g] = l0;
-    wm[warp * 16 + g + 8] = m_run[1]; wl[warp * 16 + g + 8] = l1;
-  }
 #pragma unroll
-  for (int j = 0; j < DT; ++j) {
-    const int d = j * 8 + 2 * t;
-    if (g < G) { wacc[(warp * G + g) * D + d] = o_acc[j][0]; wacc[(warp * G + g) * D + d + 1] = o_acc[j][1]; }
-    if (g + 8 < G) { wacc[(warp * G + g + 8) * D + d] = o_acc[j][2]; wacc[(warp * G + g + 8) * D + d + 1] = o_acc[j][3]; }
+  for (int nt = 0; nt < NT; ++nt) {
+    float l0 = l_run[nt][0], l1 = l_run[nt][1];
+#pragma unroll
+    for (int o = 4; o < 32; o <<= 1) {
+      l0 += __shfl_xor_sync(0xffffffffu, l0, o);
+      l1 += __shfl_xor_sync(0xffffffffu, l1, o);
+    }
+    const int h0 = nt * 8 + 2 * t;
+    if (g == 0) {
+      wm[warp * 16 + h0] = m_run[nt][0]; wl[warp * 16 + h0] = l0;
+      wm[warp * 16 + h0 + 1] = m_run[nt][1]; wl[warp * 16 + h0 + 1] = l1;
+    }
+#pragma unroll
+    for (int j = 0; j < MT; ++j) {
+      const int d = j * 16 + g;
+      if (h0 < G) { wacc[(warp * G + h0) * D + d] = o_acc[nt][j][0]; wacc[(warp * G + h0) * D + d + 8] = o_acc[nt][j][2]; }
+      if (h0 + 1 < G) { wacc[(warp * G + h0 + 1) * D + d] = o_acc[nt][j][1]; wacc[(warp * G + h0 + 1) * D + d + 8] = o_acc[nt][j][3]; }
+    }
   }
   __syncthreads();
   float* bp_num = wacc + NWARP * G * D;   // [G][D] this block's partial (cluster mode)
