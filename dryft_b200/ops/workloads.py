@@ -31,7 +31,7 @@ def run(name: str, prompts: List[List[int]], new: int, max_seq_len: int) -> dict
                              max_tokens=sum(((len(p) + new + 63) // 64 + 1) * 64 for p in prompts))
     first = t0 = t1 = 0.0
     steps = 0
-    for _ in range(2):   # the second pass is the measurement (graphs captured, libraries loaded)
+    for _ in range(3):   # the third pass is the measurement (libraries loaded by the first, the prompt step's graph captured by the second)
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         steps = 0
