@@ -159,8 +159,8 @@ def test_gemm_small_m(m, n, k_, out_dtype):
     assert torch.equal(out1[0], out[0])
 
 
-@pytest.mark.parametrize("m", [1, 8, 13])
-@pytest.mark.parametrize("n,k_", [(2560, 2560), (96, 176), (200, 1008), (4096, 1024), (208, 256), (1000, 512)])
+@pytest.mark.parametrize("m", [1, 5, 8, 13, 16])   # 5 and 13: a row of zeros stands for the rest of the 8 / 16-row operand
+@pytest.mark.parametrize("n,k_", [(2560, 2560), (96, 176), (200, 1008), (4096, 1024), (208, 256), (1000, 512), (320, 5120)])   # 5,120: one block an SM
 def test_gemm_small_m_fused_norm_residual_silu(m, n, k_):
     """The fused forms of the decode product against the plain parts: RMSNorm of the input from
     sums of squares left by an earlier product, residual add with new sums of squares, SiLU*mul."""
