@@ -9,9 +9,9 @@
 //   norm prologue (kernels/rmsnorm.py:21-39), residual epilogue with sums of squares for the next
 //   norm (rmsnorm.py:34), SiLU*mul epilogue (kernels/silu_mul.py:29-32; weights.py:98-100).
 //
-// A block of 8 warps takes 16 rows of W at a time; blocks are persistent, two per SM (one where the
-// staged activations are too large for two), each walking over every grid-th tile.  The warps split K
-// into 8 equal ranges.  A thread keeps a ring of up to ten 32-wide k steps of its two weight rows in
+// A group of 8 warps takes 16 rows of W at a time; groups are persistent, two per SM -- two blocks of one
+// group, or, with the norm on the way in, one block of two groups that share the staged activations --
+// each walking over every grid-th tile.  The warps of a group split K into 8 equal ranges.  A thread keeps a ring of up to ten 32-wide k steps of its two weight rows in
 // registers -- 16-byte loads that bypass L1, all in flight together -- and feeds them to
 // mma.sync.m16n8k16 with W as the 16 x 16 operand and 8 batch rows as the 16 x 8 operand (the k index
 // permuted identically in both operands, so that a thread's fragment is one contiguous 16-byte piece);
@@ -78,7 +78,7 @@ constexpr int KA = K + ((64 - (K * 2) % 128 + 128) % 128) / 2;  // resident row 
 // 228 KB cut), 83 us with 126 KB (one block an SM, the 132 KB cut).  So every instantiation asks for the
 // 100 KB cut (also so that neighbouring launches, which overlap, agree on it: a batch-8 step of a 2,560-wide
 // model takes 2.12 ms this way, 2.26 ms when each launch is left to the driver's choice), stages only the rows
-// there are, and runs one block an SM where two would not fit under that cut.
+// there are, once per SM, and runs one group an SM where two would not fit under that cut.
 constexpr int CARVEOUT_PCT = 43;
 constexpr size_t CARVEOUT_BYTES = 100 * 1024;
 constexpr size_t SMEM_MOST = 164 * 1024;   // one block under the 164 KB cut: L1 still holds one block's requests
@@ -104,13 +104,16 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // bytes of the partial sums, which also hold the norm's weight while the activations are normalised
-template <int MB, int PRO> __host__ __device__ constexpr size_t head_bytes() {
-  const size_t red = (size_t)WARPS * ROWS * (8 * MB + 1) * 4, nw = PRO == NORMED ? (size_t)K * 2 : 0;
+template <int MB, int PRO, int GROUPS> __host__ __device__ constexpr size_t head_bytes() {
+  const size_t red = (size_t)GROUPS * WARPS * ROWS * (8 * MB + 1) * 4, nw = PRO == NORMED ? (size_t)K * 2 : 0;
   return ((red > nw ? red : nw) + 15) / 16 * 16;
 }
 
-template <int MB, int MODE, int PRO>
-__global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
+// GROUPS = 2: two groups of 8 warps in one block, each walking tiles of its own as a block of its own would
+// (its own partial sums, its own named barrier), but sharing one copy of the staged activations, which all
+// 16 warps make together.
+template <int MB, int MODE, int PRO, int GROUPS>
+__global__ void __launch_bounds__(THREADS * GROUPS, GROUPS == 1 ? 2 : 1) gemm_decode_kernel(
     const bf16* __restrict__ A, int lda, const bf16* __restrict__ W, void* C, int ldc, int M, int N,
     const float* __restrict__ norm_w, const float* __restrict__ ss_in, int ss_parts, float eps, float* __restrict__ ss_out,
     const float* __restrict__ next_w, bf16* __restrict__ xw_out, int rs) {
@@ -123,11 +126,17 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
   // [WARPS][ROWS][MP + 1] partial sums (the norm's weight lies in the same bytes until the first tile is
   // reduced), 64 floats of inv, then the resident activations: the rs = min(M, MP) rows there are, and one
   // row of zeros behind them that stands for every row from M on
-  float* red = reinterpret_cast<float*>(smem);
-  float* inv_s = reinterpret_cast<float*>(smem + head_bytes<MB, PRO>());
+  constexpr int CT = THREADS * GROUPS;                         // threads of the block
+  const int ctid = threadIdx.x, group = GROUPS == 1 ? 0 : ctid / THREADS;
+  const int tid = ctid - group * THREADS, warp = tid >> 5, lane = tid & 31;   // within the group
+  float* red = reinterpret_cast<float*>(smem) + group * RED;
+  float* inv_s = reinterpret_cast<float*>(smem + head_bytes<MB, PRO, GROUPS>());
   bf16* a_res = reinterpret_cast<bf16*>(inv_s + SS_STRIDE);
+  auto group_sync = [&]() {
+    if (GROUPS == 1) __syncthreads();
+    else asm volatile("bar.sync %0, %1;" ::"r"(1 + group), "n"(THREADS) : "memory");
+  };
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
   const int g = lane >> 2, t = lane & 3;
   constexpr int TILE_N = MODE == SILU ? 8 : ROWS;
   const int n_tiles = (N + TILE_N - 1) / TILE_N;
@@ -146,7 +155,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
     w0 = ok0 ? W + (size_t)r0 * K + k_warp : nullptr;
     w1 = ok1 ? W + (size_t)r1 * K + k_warp : nullptr;
   };
-  int tile = blockIdx.x;
+  int tile = blockIdx.x * GROUPS + group;
   const bf16 *w0 = nullptr, *w1 = nullptr;
   if (tile < n_tiles) {
     rows_of(tile, w0, w1);
@@ -160,7 +169,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
   bf16* nw_s = reinterpret_cast<bf16*>(smem);   // the norm's weight as bfloat16 (its values are bfloat16 values held in 32-bit)
   if (NORM) {
     // the norm's weight depends on no earlier launch either: into shared memory before the wait
-    for (int i = tid; i < K / 4; i += THREADS) {
+    for (int i = ctid; i < K / 4; i += CT) {
       const float4 v = __ldg(reinterpret_cast<const float4*>(norm_w) + i);
       reinterpret_cast<__nv_bfloat162*>(nw_s)[2 * i] = __floats2bfloat162_rn(v.x, v.y);
       reinterpret_cast<__nv_bfloat162*>(nw_s)[2 * i + 1] = __floats2bfloat162_rn(v.z, v.w);
@@ -224,15 +233,15 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
     auto fetch = [&](int first) {
 #pragma unroll
       for (int u = 0; u < BATCH; ++u) {
-        const int i = first + u * THREADS;
+        const int i = first + u * CT;
         const int m = i / CHUNKS, c = i - m * CHUNKS;
         raw[u] = i < items ? ld_prev(reinterpret_cast<const uint4*>(A + (size_t)m * lda + c * 8)) : zero;
       }
     };
-    fetch(tid);
+    fetch(ctid);
     if (rs < MP)
-      for (int c = tid; c < CHUNKS; c += THREADS) *reinterpret_cast<uint4*>(a_res + (size_t)rs * KA + c * 8) = zero;
-    for (int m = warp; m < MP; m += WARPS) {
+      for (int c = ctid; c < CHUNKS; c += CT) *reinterpret_cast<uint4*>(a_res + (size_t)rs * KA + c * 8) = zero;
+    for (int m = ctid >> 5; m < MP; m += WARPS * GROUPS) {
       float s = 0.f;
       if (m < M)
         for (int p = lane; p < ss_parts; p += 32) s += ld_prev(ss_in + (size_t)p * SS_STRIDE + m);
@@ -241,11 +250,11 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
     }
     __syncthreads();   // inv_s and the norm's weight are in shared memory
 #pragma unroll 1
-    for (int first = tid; first < items; first += BATCH * THREADS) {
-      if (first != tid) fetch(first);
+    for (int first = ctid; first < items; first += BATCH * CT) {
+      if (first != ctid) fetch(first);
 #pragma unroll
       for (int u = 0; u < BATCH; ++u) {
-        const int i = first + u * THREADS;
+        const int i = first + u * CT;
         if (i >= items) break;
         const int m = i / CHUNKS, c = i - m * CHUNKS;
         uint4 out = zero;
@@ -288,13 +297,13 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
 #pragma unroll
       for (int u = 0; u < AD; ++u) ar[mb][u] = plain_a(mb, u);
   }
-  for (; tile < n_tiles; tile += gridDim.x) {
+  for (; tile < n_tiles; tile += gridDim.x * GROUPS) {
     float acc[MB][4];
 #pragma unroll
     for (int mb = 0; mb < MB; ++mb)
 #pragma unroll
       for (int i = 0; i < 4; ++i) acc[mb][i] = 0.f;
-    const int next = tile + gridDim.x;
+    const int next = tile + gridDim.x * GROUPS;
     const bool has_next = next < n_tiles;
     const bf16 *nw0 = nullptr, *nw1 = nullptr;
     if (has_next) rows_of(next, nw0, nw1);
@@ -343,7 +352,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
       }
     }
     // partial sums -> shared memory, once the tile before this one has been read from there
-    __syncthreads();
+    group_sync();
 #pragma unroll
     for (int mb = 0; mb < MB; ++mb) {
       red[(warp * ROWS + g) * (MP + 1) + mb * 8 + 2 * t] = acc[mb][0];
@@ -351,7 +360,7 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
       red[(warp * ROWS + g + 8) * (MP + 1) + mb * 8 + 2 * t] = acc[mb][2];
       red[(warp * ROWS + g + 8) * (MP + 1) + mb * 8 + 2 * t + 1] = acc[mb][3];
     }
-    __syncthreads();
+    group_sync();
     auto total = [&](int row, int m) {
       float s = 0.f;
 #pragma unroll
@@ -400,29 +409,27 @@ __global__ void __launch_bounds__(THREADS, 2) gemm_decode_kernel(
   }
 }
 
-template <int MB, int MODE, int PRO>
-int launch3(const void* A, int lda, const void* W, void* C, int ldc, int M, int N, const float* norm_w,
+template <int MB, int PRO, int GROUPS> size_t smem_of(int staged) {
+  return head_bytes<MB, PRO, GROUPS>() + SS_STRIDE * 4 + (size_t)staged * KA * 2;
+}
+template <int MB, int MODE, int PRO, int GROUPS>
+int launch4(const void* A, int lda, const void* W, void* C, int ldc, int M, int N, const float* norm_w,
             const float* ss_in, int ss_parts, float eps, float* ss_out, const float* next_w, void* xw_out, int pdl,
-            cudaStream_t st) {
-  constexpr bool NORM = PRO == NORMED;
+            int rs, int staged, int blocks_per_sm, cudaStream_t st) {
   constexpr int MP = 8 * MB;
-  const int rs = M < MP ? M : MP;                      // activation rows there are
-  const int staged = PRO == PLAIN ? 0 : (rs < MP ? rs + 1 : MP);   // and the row of zeros behind them
-  const size_t fixed = head_bytes<MB, PRO>() + SS_STRIDE * 4;
-  const size_t smem = fixed + (size_t)staged * KA * 2;
-  const size_t smem_max = fixed + (size_t)(PRO == PLAIN ? 0 : MP) * KA * 2;
+  const size_t smem = smem_of<MB, PRO, GROUPS>(staged);
+  const size_t smem_max = smem_of<MB, PRO, GROUPS>(PRO == PLAIN ? 0 : MP);
   if (smem + 1024 > SMEM_MOST) return DRYFT_ERR_UNSUPPORTED;
   static bool attr_done = false;  // per instantiation; set by an eager launch before any capture
   if (!attr_done) {
     const size_t most = smem_max + 1024 > SMEM_MOST ? SMEM_MOST - 1024 : smem_max;
-    cudaError_t e = cudaFuncSetAttribute(gemm_decode_kernel<MB, MODE, PRO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most);
+    cudaError_t e = cudaFuncSetAttribute(gemm_decode_kernel<MB, MODE, PRO, GROUPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(gemm_decode_kernel<MB, MODE, PRO>, cudaFuncAttributePreferredSharedMemoryCarveout, CARVEOUT_PCT);
+      e = cudaFuncSetAttribute(gemm_decode_kernel<MB, MODE, PRO, GROUPS>, cudaFuncAttributePreferredSharedMemoryCarveout, CARVEOUT_PCT);
     if (e != cudaSuccess) return (int)e;
     attr_done = true;
   }
-  const int blocks_per_sm = 2 * (smem + 1024) <= CARVEOUT_BYTES ? 2 : 1;
-  // Persistent blocks, two per SM, each taking every grid-th tile.  What an SM can pull from memory is
+  // Persistent blocks, each (group) taking every grid-th tile.  What an SM can pull from memory is
   // bounded by the requests its blocks keep in flight, so the tiles are spread over all SMs as evenly as
   // they go: with the usual placement (block b beside block b + SMs) the SMs' totals differ by one tile.
   static int max_blocks = 0;
@@ -433,10 +440,11 @@ int launch3(const void* A, int lda, const void* W, void* C, int ldc, int M, int 
     max_blocks = sms > 0 ? sms : 148;
   }
   const int n_tiles = MODE == SILU ? (N + 7) / 8 : (N + ROWS - 1) / ROWS;
-  const unsigned blocks = (unsigned)(n_tiles < blocks_per_sm * max_blocks ? n_tiles : blocks_per_sm * max_blocks);
+  const int want = (n_tiles + GROUPS - 1) / GROUPS;
+  const unsigned blocks = (unsigned)(want < blocks_per_sm * max_blocks ? want : blocks_per_sm * max_blocks);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(blocks);
-  cfg.blockDim = dim3(THREADS);
+  cfg.blockDim = dim3(THREADS * GROUPS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
@@ -444,10 +452,28 @@ int launch3(const void* A, int lda, const void* W, void* C, int ldc, int M, int 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_decode_kernel<MB, MODE, PRO>, (const bf16*)A, lda, (const bf16*)W, C, ldc, M,
-                                     N, norm_w, ss_in, ss_parts, eps, ss_out, next_w, (bf16*)xw_out, rs);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_decode_kernel<MB, MODE, PRO, GROUPS>, (const bf16*)A, lda, (const bf16*)W, C, ldc,
+                                     M, N, norm_w, ss_in, ss_parts, eps, ss_out, next_w, (bf16*)xw_out, rs);
   if (e != cudaSuccess) return (int)e;
   return launch_status();
+}
+// With the norm on the way in: one block an SM of two groups that share the staged rows (half the bytes to
+// stage per SM, by twice the threads: the batch-8 step of a 2,560-wide model takes 1.95 ms this way, 2.05 ms
+// with two blocks of one group; the 4,096-wide one 3.05 against 3.35 ms, where two blocks' rows do not fit
+// the cut and an SM held one); one group where even that does not fit.  Else two blocks an SM where both fit
+// under the cut, else one.
+template <int MB, int MODE, int PRO>
+int launch3(const void* A, int lda, const void* W, void* C, int ldc, int M, int N, const float* norm_w,
+            const float* ss_in, int ss_parts, float eps, float* ss_out, const float* next_w, void* xw_out, int pdl,
+            cudaStream_t st) {
+  constexpr int MP = 8 * MB;
+  const int rs = M < MP ? M : MP;                                  // activation rows there are
+  const int staged = PRO == PLAIN ? 0 : (rs < MP ? rs + 1 : MP);   // and the row of zeros behind them
+  if (PRO != NORMED && 2 * (smem_of<MB, PRO, 1>(staged) + 1024) <= CARVEOUT_BYTES)
+    return launch4<MB, MODE, PRO, 1>(A, lda, W, C, ldc, M, N, norm_w, ss_in, ss_parts, eps, ss_out, next_w, xw_out, pdl, rs, staged, 2, st);
+  if (PRO == NORMED && smem_of<MB, PRO, 2>(staged) + 1024 <= CARVEOUT_BYTES)
+    return launch4<MB, MODE, PRO, PRO == NORMED ? 2 : 1>(A, lda, W, C, ldc, M, N, norm_w, ss_in, ss_parts, eps, ss_out, next_w, xw_out, pdl, rs, staged, 1, st);
+  return launch4<MB, MODE, PRO, 1>(A, lda, W, C, ldc, M, N, norm_w, ss_in, ss_parts, eps, ss_out, next_w, xw_out, pdl, rs, staged, 1, st);
 }
 struct Args {
   const void* A; int lda; const void* W; void* C; int ldc; int M; int N;

@@ -740,9 +740,10 @@ SMALL_M_CUT_BYTES = 100 * 1024  # the shared-memory cut that csrc/gemm_decode.cu
 
 def small_m_staged_bytes(m: int, k: int) -> int:
     """Shared memory of one block of the per-size decode product with the norm on the way in (csrc/gemm_decode.cu,
-    ``launch3``): partial sums or the norm's weight, 64 factors, the ``m`` rows and a row of zeros, one reserved KB."""
+    ``launch3``): two groups' partial sums or the norm's weight, 64 factors, the ``m`` rows and a row of zeros, one
+    reserved KB."""
     mp = 8 if m <= 8 else 16
-    head = (max(8 * 16 * (mp + 1) * 4, k * 2) + 15) // 16 * 16
+    head = (max(2 * 8 * 16 * (mp + 1) * 4, k * 2) + 15) // 16 * 16   # two groups' partial sums
     rows = m + 1 if m < mp else mp
     return head + 256 + rows * (k + 32) * 2 + 1024
 
@@ -752,7 +753,7 @@ def fused_rows_supported(m: int, k: int, small_m_max: int, stream_m_max: int, no
     ``small_m_max`` rows, the tcgen05 one up to ``stream_m_max``.  ``normed``: the product has the norm on its way
     in, so its rows stay in shared memory; above 8 rows that is taken only for widths whose 16 staged rows keep
     a block under the cut that leaves L1 large enough for the weights in flight.  Measured at 9 to 16 rows:
-    width 2,560: 2.53-2.58 ms a step against 2.74-2.77 ms with the library's products; width 4,096 (ten rows
+    width 2,560: 2.38-2.40 ms a step against 2.74-2.77 ms with the library's products; width 4,096 (ten rows
     fit): 4.18 against 3.86 ms; width 5,120: 16.4 against 13.2 ms."""
     if m <= min(small_m_max, SMALL_M_LIMIT):
         if m > 8 and normed and k % 256 == 0 and small_m_staged_bytes(16, k) > SMALL_M_CUT_BYTES:

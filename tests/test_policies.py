@@ -41,7 +41,7 @@ def test_products_of_nine_to_sixteen_rows_stay_under_the_shared_memory_cut():
     assert K.fused_rows_supported(8, 5120, 16, 0, normed=True)
     assert K.fused_rows_supported(1, 8192, 16, 0, normed=True)
     # 9 to 16 rows with the norm on the way in: only widths whose 16 staged rows leave a block under 100 KB
-    assert K.small_m_staged_bytes(16, 2560) == 8704 + 256 + 16 * 2592 * 2 + 1024
+    assert K.small_m_staged_bytes(16, 2560) == 2 * 8704 + 256 + 16 * 2592 * 2 + 1024 <= K.SMALL_M_CUT_BYTES
     assert K.fused_rows_supported(16, 2560, 16, 0, normed=True)
     assert not K.fused_rows_supported(10, 4096, 16, 0, normed=True)   # ten rows would fit, sixteen do not
     assert not K.fused_rows_supported(9, 5120, 16, 0, normed=True)
