@@ -42,16 +42,14 @@ namespace {
 typedef __nv_bfloat16 bf16;
 constexpr int K = DRYFT_K;
 static_assert(K % 256 == 0, "this kernel takes inner sizes that are multiples of 256");
-constexpr int WARPS = 8;
-constexpr int THREADS = WARPS * 32;
 constexpr int ROWS = 16;
-constexpr int SPW = K / 32 / WARPS;           // 32-wide k steps per warp
+// The warps of a group (8, or 16) split K evenly: SPW 32-wide k steps a warp.
 // A thread keeps CHUNK steps of its two weight rows in registers, as a ring: the registers of the step just
 // multiplied take the step CHUNK further on, of this tile or of the block's next one, so that a warp's
 // requests never drain.  The ring's slot of a step is (step mod CHUNK) in every tile, so a tile is walked in
 // SPWP steps, a multiple of CHUNK; the steps from SPW on are empty.  CHUNK is the ring of 6 to 10 steps that
 // keeps most steps in flight after those empty ones.
-__host__ __device__ constexpr int pick_chunk(int most) {
+__host__ __device__ constexpr int pick_chunk(int SPW, int most) {
   if (SPW <= most) return SPW;
   int best = most, best_score = 0;
   for (int c = 6; c <= most; ++c) {
@@ -104,23 +102,26 @@ __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepc
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // bytes of the partial sums, which also hold the norm's weight while the activations are normalised
-template <int MB, int PRO, int GROUPS> __host__ __device__ constexpr size_t head_bytes() {
-  const size_t red = (size_t)GROUPS * WARPS * ROWS * (8 * MB + 1) * 4, nw = PRO == NORMED ? (size_t)K * 2 : 0;
+template <int MB, int PRO, int GROUPS, int GW> __host__ __device__ constexpr size_t head_bytes() {
+  const size_t red = (size_t)GROUPS * GW * ROWS * (8 * MB + 1) * 4, nw = PRO == NORMED ? (size_t)K * 2 : 0;
   return ((red > nw ? red : nw) + 15) / 16 * 16;
 }
 
 // GROUPS = 2: two groups of 8 warps in one block, each walking tiles of its own as a block of its own would
 // (its own partial sums, its own named barrier), but sharing one copy of the staged activations, which all
 // 16 warps make together.
-template <int MB, int MODE, int PRO, int GROUPS>
-__global__ void __launch_bounds__(THREADS * GROUPS, GROUPS == 1 ? 2 : 1) gemm_decode_kernel(
+// GW = 16: the 16 warps of the block split K of ONE tile 16 ways (inner sizes of at least 8 steps a warp then):
+// the narrow products, whose tiles are about as many as the SMs, keep twice the requests in flight per SM.
+template <int MB, int MODE, int PRO, int GROUPS, int GW>
+__global__ void __launch_bounds__(GW * 32 * GROUPS, GW * GROUPS == 8 ? 2 : 1) gemm_decode_kernel(
     const bf16* __restrict__ A, int lda, const bf16* __restrict__ W, void* C, int ldc, int M, int N,
     const float* __restrict__ norm_w, const float* __restrict__ ss_in, int ss_parts, float eps, float* __restrict__ ss_out,
     const float* __restrict__ next_w, bf16* __restrict__ xw_out, int rs) {
   constexpr bool NORM = PRO == NORMED;
   constexpr int MP = 8 * MB;
+  constexpr int WARPS = GW, THREADS = GW * 32, SPW = K / 32 / GW;   // of a group: shadow the 8-warp constants
   constexpr int RED = WARPS * ROWS * (MP + 1);
-  constexpr int CHUNK = pick_chunk(MB == 2 && PRO == PLAIN ? 8 : 10);
+  constexpr int CHUNK = pick_chunk(SPW, MB == 2 && PRO == PLAIN ? 8 : 10);
   constexpr int SPWP = (SPW + CHUNK - 1) / CHUNK * CHUNK;
   extern __shared__ __align__(16) unsigned char smem[];
   // [WARPS][ROWS][MP + 1] partial sums (the norm's weight lies in the same bytes until the first tile is
@@ -130,11 +131,11 @@ __global__ void __launch_bounds__(THREADS * GROUPS, GROUPS == 1 ? 2 : 1) gemm_de
   const int ctid = threadIdx.x, group = GROUPS == 1 ? 0 : ctid / THREADS;
   const int tid = ctid - group * THREADS, warp = tid >> 5, lane = tid & 31;   // within the group
   float* red = reinterpret_cast<float*>(smem) + group * RED;
-  float* inv_s = reinterpret_cast<float*>(smem + head_bytes<MB, PRO, GROUPS>());
+  float* inv_s = reinterpret_cast<float*>(smem + head_bytes<MB, PRO, GROUPS, GW>());
   bf16* a_res = reinterpret_cast<bf16*>(inv_s + SS_STRIDE);
   auto group_sync = [&]() {
     if (GROUPS == 1) __syncthreads();
-    else asm volatile("bar.sync %0, %1;" ::"r"(1 + group), "n"(THREADS) : "memory");
+    else asm volatile("bar.sync %0, %1;" ::"r"(1 + group), "n"(GW * 32) : "memory");
   };
 
   const int g = lane >> 2, t = lane & 3;
@@ -409,42 +410,46 @@ __global__ void __launch_bounds__(THREADS * GROUPS, GROUPS == 1 ? 2 : 1) gemm_de
   }
 }
 
-template <int MB, int PRO, int GROUPS> size_t smem_of(int staged) {
-  return head_bytes<MB, PRO, GROUPS>() + SS_STRIDE * 4 + (size_t)staged * KA * 2;
+int sm_count() {
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0, n = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    sms = n > 0 ? n : 148;
+  }
+  return sms;
 }
-template <int MB, int MODE, int PRO, int GROUPS>
+template <int MB, int PRO, int GROUPS, int GW> size_t smem_of(int staged) {
+  return head_bytes<MB, PRO, GROUPS, GW>() + SS_STRIDE * 4 + (size_t)staged * KA * 2;
+}
+template <int MB, int MODE, int PRO, int GROUPS, int GW>
 int launch4(const void* A, int lda, const void* W, void* C, int ldc, int M, int N, const float* norm_w,
             const float* ss_in, int ss_parts, float eps, float* ss_out, const float* next_w, void* xw_out, int pdl,
             int rs, int staged, int blocks_per_sm, cudaStream_t st) {
   constexpr int MP = 8 * MB;
-  const size_t smem = smem_of<MB, PRO, GROUPS>(staged);
-  const size_t smem_max = smem_of<MB, PRO, GROUPS>(PRO == PLAIN ? 0 : MP);
+  const size_t smem = smem_of<MB, PRO, GROUPS, GW>(staged);
+  const size_t smem_max = smem_of<MB, PRO, GROUPS, GW>(PRO == PLAIN ? 0 : MP);
   if (smem + 1024 > SMEM_MOST) return DRYFT_ERR_UNSUPPORTED;
   static bool attr_done = false;  // per instantiation; set by an eager launch before any capture
   if (!attr_done) {
     const size_t most = smem_max + 1024 > SMEM_MOST ? SMEM_MOST - 1024 : smem_max;
-    cudaError_t e = cudaFuncSetAttribute(gemm_decode_kernel<MB, MODE, PRO, GROUPS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most);
+    cudaError_t e = cudaFuncSetAttribute(gemm_decode_kernel<MB, MODE, PRO, GROUPS, GW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most);
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(gemm_decode_kernel<MB, MODE, PRO, GROUPS>, cudaFuncAttributePreferredSharedMemoryCarveout, CARVEOUT_PCT);
+      e = cudaFuncSetAttribute(gemm_decode_kernel<MB, MODE, PRO, GROUPS, GW>, cudaFuncAttributePreferredSharedMemoryCarveout, CARVEOUT_PCT);
     if (e != cudaSuccess) return (int)e;
     attr_done = true;
   }
   // Persistent blocks, each (group) taking every grid-th tile.  What an SM can pull from memory is
   // bounded by the requests its blocks keep in flight, so the tiles are spread over all SMs as evenly as
   // they go: with the usual placement (block b beside block b + SMs) the SMs' totals differ by one tile.
-  static int max_blocks = 0;
-  if (max_blocks == 0) {
-    int dev = 0, sms = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    max_blocks = sms > 0 ? sms : 148;
-  }
+  const int max_blocks = sm_count();
   const int n_tiles = MODE == SILU ? (N + 7) / 8 : (N + ROWS - 1) / ROWS;
   const int want = (n_tiles + GROUPS - 1) / GROUPS;
   const unsigned blocks = (unsigned)(want < blocks_per_sm * max_blocks ? want : blocks_per_sm * max_blocks);
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(blocks);
-  cfg.blockDim = dim3(THREADS * GROUPS);
+  cfg.blockDim = dim3(GW * 32 * GROUPS);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[1];
@@ -452,7 +457,7 @@ int launch4(const void* A, int lda, const void* W, void* C, int ldc, int M, int 
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_decode_kernel<MB, MODE, PRO, GROUPS>, (const bf16*)A, lda, (const bf16*)W, C, ldc,
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_decode_kernel<MB, MODE, PRO, GROUPS, GW>, (const bf16*)A, lda, (const bf16*)W, C, ldc,
                                      M, N, norm_w, ss_in, ss_parts, eps, ss_out, next_w, (bf16*)xw_out, rs);
   if (e != cudaSuccess) return (int)e;
   return launch_status();
@@ -469,11 +474,15 @@ int launch3(const void* A, int lda, const void* W, void* C, int ldc, int M, int 
   constexpr int MP = 8 * MB;
   const int rs = M < MP ? M : MP;                                  // activation rows there are
   const int staged = PRO == PLAIN ? 0 : (rs < MP ? rs + 1 : MP);   // and the row of zeros behind them
-  if (PRO != NORMED && 2 * (smem_of<MB, PRO, 1>(staged) + 1024) <= CARVEOUT_BYTES)
-    return launch4<MB, MODE, PRO, 1>(A, lda, W, C, ldc, M, N, norm_w, ss_in, ss_parts, eps, ss_out, next_w, xw_out, pdl, rs, staged, 2, st);
-  if (PRO == NORMED && smem_of<MB, PRO, 2>(staged) + 1024 <= CARVEOUT_BYTES)
-    return launch4<MB, MODE, PRO, PRO == NORMED ? 2 : 1>(A, lda, W, C, ldc, M, N, norm_w, ss_in, ss_parts, eps, ss_out, next_w, xw_out, pdl, rs, staged, 1, st);
-  return launch4<MB, MODE, PRO, 1>(A, lda, W, C, ldc, M, N, norm_w, ss_in, ss_parts, eps, ss_out, next_w, xw_out, pdl, rs, staged, 1, st);
+#define DRYFT_GO(GROUPS, GW, PER_SM) \
+  launch4<MB, MODE, PRO, GROUPS, GW>(A, lda, W, C, ldc, M, N, norm_w, ss_in, ss_parts, eps, ss_out, next_w, xw_out, pdl, rs, staged, PER_SM, st)
+  constexpr int WIDE = (K % 512 == 0 && K / 512 >= 8 && PRO != SCALED) ? 16 : 8;   // 16 warps on one tile where a warp keeps 8 steps
+  const int n_tiles = MODE == SILU ? (N + 7) / 8 : (N + ROWS - 1) / ROWS;
+  if (WIDE == 16 && n_tiles >= 2 * sm_count() && smem_of<MB, PRO, 1, WIDE>(staged) + 1024 <= CARVEOUT_BYTES) return DRYFT_GO(1, WIDE, 1);
+  if (PRO != NORMED && 2 * (smem_of<MB, PRO, 1, 8>(staged) + 1024) <= CARVEOUT_BYTES) return DRYFT_GO(1, 8, 2);
+  if (PRO == NORMED && smem_of<MB, PRO, 2, 8>(staged) + 1024 <= CARVEOUT_BYTES) return DRYFT_GO((PRO == NORMED ? 2 : 1), 8, 1);
+  return DRYFT_GO(1, 8, 1);
+#undef DRYFT_GO
 }
 struct Args {
   const void* A; int lda; const void* W; void* C; int ldc; int M; int N;

@@ -142,7 +142,8 @@ def test_gemm_f32(m, n, k_):
 
 
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
-@pytest.mark.parametrize("n,k_", [(2560, 2560), (331, 96), (19, 4096), (6144, 1008), (48, 16), (160, 9728), (100, 256), (333, 1024)])
+@pytest.mark.parametrize("n,k_", [(2560, 2560), (331, 96), (19, 4096), (6144, 1008), (48, 16), (160, 9728), (100, 256), (333, 1024),
+                                  (4750, 4096)])   # the last: tiles for every SM twice over, so 16 warps share a tile
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_gemm_small_m(m, n, k_, out_dtype):
     k = K()
@@ -160,7 +161,7 @@ def test_gemm_small_m(m, n, k_, out_dtype):
 
 
 @pytest.mark.parametrize("m", [1, 5, 8, 13, 16])   # 5 and 13: a row of zeros stands for the rest of the 8 / 16-row operand
-@pytest.mark.parametrize("n,k_", [(2560, 2560), (96, 176), (200, 1008), (4096, 1024), (208, 256), (1000, 512), (320, 5120)])   # 5,120: one block an SM
+@pytest.mark.parametrize("n,k_", [(2560, 2560), (96, 176), (200, 1008), (4096, 1024), (208, 256), (1000, 512), (320, 5120), (4736, 4096)])   # 5,120: one block an SM; 4,736 x 4,096: 16 warps a tile
 def test_gemm_small_m_fused_norm_residual_silu(m, n, k_):
     """The fused forms of the decode product against the plain parts: RMSNorm of the input from
     sums of squares left by an earlier product, residual add with new sums of squares, SiLU*mul."""
