@@ -20,7 +20,8 @@
 // activations are made once per block and stay in shared memory (the M rows there are and one row of
 // zeros for the rest of the operand); otherwise they are read through L2, a few steps ahead.  The 8
 // partial sums are added in warp order through shared memory: a row's result depends neither on the
-// other rows nor on M.
+// other rows nor on M (the split of K is chosen by the sizes of the product and by whether M is up to 8 or
+// up to 16, never by M itself).
 //
 // The norm can also be split between two launches, which takes it off the consumer's critical path: a
 // residual product that knows the next norm's weight w leaves, beside the new stream x, the weighted
@@ -478,7 +479,10 @@ int launch3(const void* A, int lda, const void* W, void* C, int ldc, int M, int 
   launch4<MB, MODE, PRO, GROUPS, GW>(A, lda, W, C, ldc, M, N, norm_w, ss_in, ss_parts, eps, ss_out, next_w, xw_out, pdl, rs, staged, PER_SM, st)
   constexpr int WIDE = (K % 512 == 0 && K / 512 >= 8 && PRO != SCALED) ? 16 : 8;   // 16 warps on one tile where a warp keeps 8 steps
   const int n_tiles = MODE == SILU ? (N + 7) / 8 : (N + ROWS - 1) / ROWS;
-  if (WIDE == 16 && n_tiles >= 2 * sm_count() && smem_of<MB, PRO, 1, WIDE>(staged) + 1024 <= CARVEOUT_BYTES) return DRYFT_GO(1, WIDE, 1);
+  // (decided by what 8 / 16 rows would need, not by M: the split of K, and with it the order of the sums,
+  // is then the same for every M up to 8, and for every M from 9 to 16)
+  if (WIDE == 16 && n_tiles >= 2 * sm_count() && smem_of<MB, PRO, 1, WIDE>(PRO == PLAIN ? 0 : MP) + 1024 <= CARVEOUT_BYTES)
+    return DRYFT_GO(1, WIDE, 1);
   if (PRO != NORMED && 2 * (smem_of<MB, PRO, 1, 8>(staged) + 1024) <= CARVEOUT_BYTES) return DRYFT_GO(1, 8, 2);
   if (PRO == NORMED && smem_of<MB, PRO, 2, 8>(staged) + 1024 <= CARVEOUT_BYTES) return DRYFT_GO((PRO == NORMED ? 2 : 1), 8, 1);
   return DRYFT_GO(1, 8, 1);
