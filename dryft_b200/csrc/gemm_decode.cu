@@ -111,8 +111,9 @@ template <int MB, int PRO, int GROUPS, int GW> __host__ __device__ constexpr siz
 // GROUPS = 2: two groups of 8 warps in one block, each walking tiles of its own as a block of its own would
 // (its own partial sums, its own named barrier), but sharing one copy of the staged activations, which all
 // 16 warps make together.
-// GW = 16: the 16 warps of the block split K of ONE tile 16 ways (inner sizes of at least 8 steps a warp then):
-// the narrow products, whose tiles are about as many as the SMs, keep twice the requests in flight per SM.
+// GW = 16: the 16 warps of the block split K of ONE tile 16 ways, for inner sizes that still leave a warp 8 steps
+// or more and products with tiles for every SM twice over: one staged copy, one tile's epilogue at a time, and
+// half as long a wait for the slowest block at the end.
 template <int MB, int MODE, int PRO, int GROUPS, int GW>
 __global__ void __launch_bounds__(GW * 32 * GROUPS, GW * GROUPS == 8 ? 2 : 1) gemm_decode_kernel(
     const bf16* __restrict__ A, int lda, const bf16* __restrict__ W, void* C, int ldc, int M, int N,
@@ -120,7 +121,7 @@ __global__ void __launch_bounds__(GW * 32 * GROUPS, GW * GROUPS == 8 ? 2 : 1) ge
     const float* __restrict__ next_w, bf16* __restrict__ xw_out, int rs) {
   constexpr bool NORM = PRO == NORMED;
   constexpr int MP = 8 * MB;
-  constexpr int WARPS = GW, THREADS = GW * 32, SPW = K / 32 / GW;   // of a group: shadow the 8-warp constants
+  constexpr int WARPS = GW, THREADS = GW * 32, SPW = K / 32 / GW;   // of a group; SPW: 32-wide k steps a warp
   constexpr int RED = WARPS * ROWS * (MP + 1);
   constexpr int CHUNK = pick_chunk(SPW, MB == 2 && PRO == PLAIN ? 8 : 10);
   constexpr int SPWP = (SPW + CHUNK - 1) / CHUNK * CHUNK;
