@@ -30,6 +30,18 @@ def pytest_collection_modifyitems(config, items):
             item.add_marker(skip)
 
 
+@pytest.fixture(autouse=True)
+def _seed_from_the_tests_name(request):
+    """Every test draws its random inputs from a generator seeded by its own name, so that what a test sees
+    does not depend on which tests ran before it, and a failure can be reproduced alone."""
+    import zlib
+
+    import torch
+
+    torch.manual_seed(zlib.crc32(request.node.nodeid.encode()))   # seeds the CPU and every CUDA generator
+    yield
+
+
 @pytest.fixture(scope="session")
 def model_dirs(tmp_path_factory):
     """{config name: model folder} for the tiny test configurations, random weights."""
